@@ -1,0 +1,375 @@
+// C ABI of libcame_b200: descriptor validation, workspace layout, work lists, step scheduling.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <tuple>
+#include <vector>
+
+#include "came_b200.h"
+#include "launch.h"
+
+using namespace came;
+
+namespace {
+
+constexpr int MAX_GROUPS = 64;
+constexpr size_t ALIGN = 256;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+inline size_t align_up(size_t x, size_t a = ALIGN) { return (x + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+struct LaunchItem {
+    int kernel;
+    KernelKey key;
+    size_t work_off;   // in Work units from the start of the work region
+    int n;
+};
+
+// vector-path eligibility of a tensor for each kernel family
+struct VecFlags {
+    bool k;      // gradient reductions: runs of 8
+    bool p2;     // momentum pass: runs of 16 over g and m
+    bool p3;     // apply pass: runs of 16 over m and p
+    bool flat;   // flat apply: runs of 8 over g, m, p
+    bool operator==(const VecFlags& o) const { return k == o.k && p2 == o.p2 && p3 == o.p3 && flat == o.flat; }
+};
+
+VecFlags vec_flags(const CameTensorDesc& d) {
+    VecFlags v{false, false, false, false};
+    if (d.cols == 0) return v;
+    const bool c8 = d.cols % 8 == 0, c16 = d.cols % 16 == 0;
+    v.k = c8 && aligned16(d.g);
+    v.p2 = c16 && aligned16(d.g) && aligned16(d.m);
+    v.p3 = c16 && aligned16(d.p) && aligned16(d.m);
+    v.flat = c8 && aligned16(d.g) && aligned16(d.p) && (reinterpret_cast<uintptr_t>(d.m) & 7u) == 0;
+    return v;
+}
+
+struct Geometry {
+    int64_t R, C;
+    int tiles_r, tiles_c, ptiles_r, ptiles_c, nbR, nbC;
+    int64_t flat_chunks;
+    size_t floats;   // scratch floats of this tensor
+};
+
+Geometry geometry(const CameTensorDesc& d) {
+    Geometry g{};
+    g.R = d.rows;
+    g.C = d.cols;
+    g.nbR = (int)cdiv(g.R, QBLOCK);
+    if (d.cols == 0) {
+        g.floats = align_up((size_t)g.nbR, 4);
+        return g;
+    }
+    g.nbC = (int)cdiv(g.C, QBLOCK);
+    g.tiles_r = (int)cdiv(g.R, K_TR);
+    g.tiles_c = (int)cdiv(g.C, K_TC);
+    g.ptiles_r = (int)cdiv(g.R, P_TR);
+    g.ptiles_c = (int)cdiv(g.C, P_TC);
+    g.flat_chunks = cdiv(cdiv(g.R * g.C, QBLOCK), FLAT_BLOCKS_PER_CTA);
+    return g;
+}
+
+// carve the per-tensor float scratch; base == nullptr computes sizes only
+size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* out) {
+    size_t off = 0;
+    auto take = [&](size_t n) -> float* {
+        float* p = base ? base + off : nullptr;
+        off += align_up(n, 4);
+        return p;
+    };
+    Scratch s{};
+    s.nbR = g.nbR;
+    if (d.cols == 0) {
+        s.spart = take((size_t)g.nbR);
+    } else {
+        s.nbC = g.nbC;
+        s.tiles_r = g.tiles_r; s.tiles_c = g.tiles_c;
+        s.ptiles_r = g.ptiles_r; s.ptiles_c = g.ptiles_c;
+        s.vr = take((size_t)g.R); s.vc = take((size_t)g.C);
+        s.Rr = take((size_t)g.R); s.Rc = take((size_t)g.C);
+        s.rowblk = take((size_t)g.nbR); s.rowblk2 = take((size_t)g.nbR);
+        s.scal = take(4);
+        s.rowpart = take((size_t)std::max(g.tiles_c, g.ptiles_c) * (size_t)g.R);
+        s.colpart = take((size_t)std::max(g.tiles_r, g.ptiles_r) * (size_t)g.C);
+        s.spart = take((size_t)g.tiles_r * (size_t)g.tiles_c);
+        s.fac = d.mode == CAME_MODE_FLAT8 ? take(2 * (size_t)(g.R + g.C)) : nullptr;
+    }
+    if (out) *out = s;
+    return off;
+}
+
+int validate(const CameTensorDesc& d, int i) {
+    if (!d.p || !d.g || !d.m) return fail(CAME_E_INVALID, "tensor %d: p, g and m must be non-null", i);
+    if (d.rows <= 0 || d.cols < 0) return fail(CAME_E_INVALID, "tensor %d: bad shape [%lld, %lld]", i, (long long)d.rows, (long long)d.cols);
+    if (d.rows > 0x7fffffffLL || d.cols > 0x7fffffffLL) return fail(CAME_E_UNSUPPORTED, "tensor %d: dimension above 2^31-1", i);
+    if (d.mode < CAME_MODE_FP32 || d.mode > CAME_MODE_FLAT8) return fail(CAME_E_INVALID, "tensor %d: bad mode %d", i, d.mode);
+    if (d.p_dtype < CAME_DT_F32 || d.p_dtype > CAME_DT_BF16 || d.g_dtype < CAME_DT_F32 || d.g_dtype > CAME_DT_BF16)
+        return fail(CAME_E_INVALID, "tensor %d: bad dtype", i);
+    if (d.group < 0 || d.group >= MAX_GROUPS) return fail(CAME_E_INVALID, "tensor %d: group %d outside [0, %d)", i, d.group, MAX_GROUPS);
+    const bool quant = d.mode != CAME_MODE_FP32;
+    if (quant && !d.m_absmax) return fail(CAME_E_INVALID, "tensor %d: 8-bit exp_avg needs m_absmax", i);
+    if (!d.sq_row || (quant && !d.sq_row_absmax)) return fail(CAME_E_INVALID, "tensor %d: missing exp_avg_sq state", i);
+    if (d.cols == 0) {
+        if (d.mode == CAME_MODE_TILE8) return fail(CAME_E_INVALID, "tensor %d: 1-D tensors use CAME_MODE_FLAT8 or CAME_MODE_FP32", i);
+        return CAME_OK;
+    }
+    if (!d.sq_col || !d.res_row || !d.res_col) return fail(CAME_E_INVALID, "tensor %d: missing factored state", i);
+    if (quant && (!d.sq_col_absmax || !d.res_row_absmax || !d.res_col_absmax))
+        return fail(CAME_E_INVALID, "tensor %d: missing factored absmax", i);
+    return CAME_OK;
+}
+
+struct Layout {
+    size_t off_descs, off_scr, off_hyp, off_work, off_float, total;
+    size_t n_work;
+};
+
+size_t count_work(const CameTensorDesc* descs, int n) {
+    size_t w = 0;
+    for (int i = 0; i < n; ++i) {
+        const Geometry g = geometry(descs[i]);
+        if (descs[i].cols == 0) {
+            w += 2 * (size_t)g.nbR;
+            continue;
+        }
+        w += 2 * (size_t)g.tiles_r * g.tiles_c;      // sq_partials, sumsq
+        w += 2 * (size_t)(g.nbR + g.nbC);            // two vector finalizes
+        w += 1;                                      // s_finalize
+        w += (size_t)g.ptiles_r * g.ptiles_c;        // moment
+        if (descs[i].mode == CAME_MODE_FLAT8) w += (size_t)(g.nbR + g.nbC) + (size_t)g.flat_chunks;
+        else w += (size_t)g.ptiles_r * g.ptiles_c;   // apply
+    }
+    return w;
+}
+
+Layout layout(const CameTensorDesc* descs, int n) {
+    Layout L{};
+    size_t off = 0;
+    L.off_descs = off; off = align_up(off + (size_t)n * sizeof(CameTensorDesc));
+    L.off_scr = off;   off = align_up(off + (size_t)n * sizeof(Scratch));
+    L.off_hyp = off;   off = align_up(off + (size_t)MAX_GROUPS * sizeof(CameHyper));
+    L.n_work = count_work(descs, n);
+    L.off_work = off;  off = align_up(off + L.n_work * sizeof(Work));
+    L.off_float = off;
+    size_t fl = 0;
+    for (int i = 0; i < n; ++i) fl += align_up(carve(descs[i], geometry(descs[i]), nullptr, nullptr), 64);
+    off = align_up(off + fl * sizeof(float));
+    L.total = off;
+    return L;
+}
+
+}  // namespace
+
+struct came_plan {
+    int n_tensors = 0;
+    std::vector<CameTensorDesc> descs;
+    std::vector<VecFlags> vflags;
+    char* ws = nullptr;
+    Layout L{};
+    std::vector<LaunchItem> launches;
+    int last_launches = 0;
+};
+
+extern "C" {
+
+int came_b200_version(void) { return CAME_B200_VERSION; }
+const char* came_b200_last_error(void) { return g_err; }
+
+int came_b200_quantize_blockwise(const float* src, void* q, float* absmax, int64_t n, int is_signed, came_stream_t stream) {
+    if (!q || !absmax || n < 0 || (n > 0 && !src)) return fail(CAME_E_INVALID, "quantize_blockwise: null pointer or negative size");
+    const cudaError_t e = launch_quantize_blockwise(src, q, absmax, n, is_signed != 0, (cudaStream_t)stream);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "quantize_blockwise: %s", cudaGetErrorString(e));
+}
+
+int came_b200_dequantize_blockwise(const void* q, const float* absmax, float* dst, int64_t n, int is_signed, came_stream_t stream) {
+    if (n < 0 || (n > 0 && (!q || !absmax || !dst))) return fail(CAME_E_INVALID, "dequantize_blockwise: null pointer or negative size");
+    const cudaError_t e = launch_dequantize_blockwise(q, absmax, dst, n, is_signed != 0, (cudaStream_t)stream);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "dequantize_blockwise: %s", cudaGetErrorString(e));
+}
+
+int came_b200_quantize_tile16(const float* src, int8_t* q, float* absmax, int64_t rows, int64_t cols, came_stream_t stream) {
+    if (!src || !q || !absmax || rows <= 0 || cols <= 0) return fail(CAME_E_INVALID, "quantize_tile16: bad argument");
+    const cudaError_t e = launch_quantize_tile16(src, q, absmax, rows, cols, (cudaStream_t)stream);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "quantize_tile16: %s", cudaGetErrorString(e));
+}
+
+int came_b200_dequantize_tile16(const int8_t* q, const float* absmax, float* dst, int64_t rows, int64_t cols, came_stream_t stream) {
+    if (!dst || !q || !absmax || rows <= 0 || cols <= 0) return fail(CAME_E_INVALID, "dequantize_tile16: bad argument");
+    const cudaError_t e = launch_dequantize_tile16(q, absmax, dst, rows, cols, (cudaStream_t)stream);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "dequantize_tile16: %s", cudaGetErrorString(e));
+}
+
+size_t came_b200_workspace_bytes(const CameTensorDesc* descs, int n_tensors) {
+    if (!descs || n_tensors <= 0) return 0;
+    for (int i = 0; i < n_tensors; ++i)
+        if (validate(descs[i], i) != CAME_OK) return 0;
+    return layout(descs, n_tensors).total;
+}
+
+int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* workspace, size_t workspace_bytes,
+                          came_stream_t stream, came_plan_t** out) {
+    if (!out) return fail(CAME_E_INVALID, "plan_create: out is null");
+    *out = nullptr;
+    if (!descs || n_tensors <= 0) return fail(CAME_E_INVALID, "plan_create: no tensors");
+    for (int i = 0; i < n_tensors; ++i) {
+        const int rc = validate(descs[i], i);
+        if (rc != CAME_OK) return rc;
+    }
+    const Layout L = layout(descs, n_tensors);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % ALIGN) != 0)
+        return fail(CAME_E_WORKSPACE, "plan_create: workspace must be non-null and %zu-byte aligned", ALIGN);
+    if (workspace_bytes < L.total)
+        return fail(CAME_E_WORKSPACE, "plan_create: workspace of %zu bytes, %zu needed", workspace_bytes, L.total);
+
+    came_plan* plan = new (std::nothrow) came_plan();
+    if (!plan) return fail(CAME_E_INVALID, "plan_create: out of host memory");
+    plan->n_tensors = n_tensors;
+    plan->descs.assign(descs, descs + n_tensors);
+    plan->ws = static_cast<char*>(workspace);
+    plan->L = L;
+    plan->vflags.resize(n_tensors);
+
+    std::vector<Scratch> scr(n_tensors);
+    std::vector<Geometry> geo(n_tensors);
+    float* fbase = reinterpret_cast<float*>(plan->ws + L.off_float);
+    size_t foff = 0;
+    for (int i = 0; i < n_tensors; ++i) {
+        geo[i] = geometry(descs[i]);
+        plan->vflags[i] = vec_flags(descs[i]);
+        foff += align_up(carve(descs[i], geo[i], fbase + foff, &scr[i]), 64);
+    }
+
+    // work lists, one per (kernel, template key), in execution order
+    std::vector<Work> work;
+    work.reserve(L.n_work);
+    using Key = std::tuple<int, int, int, int>;   // g, p, mode, vec
+    auto build = [&](int kernel, auto select, auto keyof, auto count) {
+        std::map<Key, std::vector<int>> groups;
+        for (int i = 0; i < n_tensors; ++i)
+            if (select(i)) groups[keyof(i)].push_back(i);
+        for (auto& kv : groups) {
+            LaunchItem it{};
+            it.kernel = kernel;
+            it.key = KernelKey{std::get<0>(kv.first), std::get<1>(kv.first), std::get<2>(kv.first), std::get<3>(kv.first) != 0};
+            it.work_off = work.size();
+            for (int i : kv.second) {
+                const int64_t c = count(i);
+                for (int64_t t = 0; t < c; ++t) work.push_back(Work{i, (int32_t)t});
+            }
+            it.n = (int)(work.size() - it.work_off);
+            if (it.n > 0) plan->launches.push_back(it);
+        }
+    };
+    const CameTensorDesc* D = descs;
+    auto is1d = [&](int i) { return D[i].cols == 0; };
+    auto is2d = [&](int i) { return D[i].cols != 0; };
+    auto isflat = [&](int i) { return D[i].cols != 0 && D[i].mode == CAME_MODE_FLAT8; };
+    auto notflat = [&](int i) { return D[i].cols != 0 && D[i].mode != CAME_MODE_FLAT8; };
+    auto nokey = [&](int) { return Key{0, 0, 0, 0}; };
+    const auto& vf = plan->vflags;
+
+    build(KID_NF_PARTIAL, is1d, [&](int i) { return Key{D[i].g_dtype, 0, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
+    build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
+    build(KID_SQ_PARTIALS, is2d, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
+          [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
+    build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
+    build(KID_SUMSQ, is2d, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
+          [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
+    build(KID_S_FINALIZE, is2d, nokey, [&](int) { return (int64_t)1; });
+    build(KID_MOMENT, is2d, [&](int i) { return Key{D[i].g_dtype, 0, D[i].mode, vf[i].p2}; },
+          [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
+    build(KID_RES_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
+    build(KID_APPLY, notflat, [&](int i) { return Key{0, D[i].p_dtype, D[i].mode, vf[i].p3}; },
+          [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
+    build(KID_FACTORS, isflat, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
+    build(KID_APPLY_FLAT, isflat, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, vf[i].flat}; },
+          [&](int i) { return geo[i].flat_chunks; });
+
+    if (work.size() > L.n_work) {
+        delete plan;
+        return fail(CAME_E_INVALID, "plan_create: internal work-list overflow (%zu > %zu)", work.size(), L.n_work);
+    }
+
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(plan->ws + L.off_descs, plan->descs.data(), (size_t)n_tensors * sizeof(CameTensorDesc),
+                                    cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(plan->ws + L.off_scr, scr.data(), (size_t)n_tensors * sizeof(Scratch), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess && !work.empty())
+        e = cudaMemcpyAsync(plan->ws + L.off_work, work.data(), work.size() * sizeof(Work), cudaMemcpyHostToDevice, st);
+    // the host vectors above die at return: wait for the copies
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        delete plan;
+        return fail(CAME_E_CUDA, "plan_create: %s", cudaGetErrorString(e));
+    }
+    *out = plan;
+    return CAME_OK;
+}
+
+void came_b200_plan_destroy(came_plan_t* plan) { delete plan; }
+
+int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* const* p, int n_tensors, came_stream_t stream) {
+    if (!plan) return fail(CAME_E_INVALID, "set_pointers: plan is null");
+    if (n_tensors != plan->n_tensors) return fail(CAME_E_INVALID, "set_pointers: %d tensors given, plan has %d", n_tensors, plan->n_tensors);
+    if (!g && !p) return CAME_OK;
+    std::vector<CameTensorDesc> next = plan->descs;
+    for (int i = 0; i < n_tensors; ++i) {
+        if (g) next[i].g = g[i];
+        if (p) next[i].p = p[i];
+        if (!next[i].g || !next[i].p) return fail(CAME_E_INVALID, "set_pointers: tensor %d: null pointer", i);
+        if (!(vec_flags(next[i]) == plan->vflags[i]))
+            return fail(CAME_E_INVALID, "set_pointers: tensor %d changes 16-byte alignment class; create a new plan", i);
+    }
+    plan->descs.swap(next);
+    const cudaError_t e = cudaMemcpyAsync(plan->ws + plan->L.off_descs, plan->descs.data(),
+                                          (size_t)n_tensors * sizeof(CameTensorDesc), cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "set_pointers: %s", cudaGetErrorString(e));
+}
+
+int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, came_stream_t stream) {
+    if (!plan || !hypers) return fail(CAME_E_INVALID, "step: null argument");
+    if (n_groups <= 0 || n_groups > MAX_GROUPS) return fail(CAME_E_INVALID, "step: n_groups %d outside [1, %d]", n_groups, MAX_GROUPS);
+    for (const auto& d : plan->descs)
+        if (d.group >= n_groups) return fail(CAME_E_INVALID, "step: a tensor refers to group %d, %d given", d.group, n_groups);
+    for (int i = 0; i < n_groups; ++i) {
+        if (!(hypers[i].clip_threshold > 0.0f)) return fail(CAME_E_INVALID, "step: group %d: clip_threshold must be > 0", i);
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(plan->ws + plan->L.off_hyp, hypers, (size_t)n_groups * sizeof(CameHyper),
+                                    cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: hyper-parameter upload: %s", cudaGetErrorString(e));
+    StepArgs a{reinterpret_cast<const CameTensorDesc*>(plan->ws + plan->L.off_descs),
+               reinterpret_cast<const Scratch*>(plan->ws + plan->L.off_scr),
+               reinterpret_cast<const CameHyper*>(plan->ws + plan->L.off_hyp)};
+    const Work* wbase = reinterpret_cast<const Work*>(plan->ws + plan->L.off_work);
+    int launches = 0;
+    for (const LaunchItem& it : plan->launches) {
+        e = (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY)
+                ? launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st)
+                : launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
+        if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: kernel %d: %s", it.kernel, cudaGetErrorString(e));
+        ++launches;
+    }
+    plan->last_launches = launches;
+    return CAME_OK;
+}
+
+int came_b200_plan_last_launches(const came_plan_t* plan) { return plan ? plan->last_launches : 0; }
+
+}  // extern "C"

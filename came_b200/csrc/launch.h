@@ -1,0 +1,55 @@
+// Internal interface between the C-ABI layer (plan / step) and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "came_b200.h"
+#include "common.cuh"
+
+namespace came {
+
+struct StepArgs {
+    const CameTensorDesc* descs;   // device copy of the descriptor table
+    const Scratch* scr;            // device, one per tensor
+    const CameHyper* hyp;          // device, one per param_group
+};
+
+// which template instance a work list is launched with
+struct KernelKey {
+    int g_dtype;
+    int p_dtype;
+    int mode;
+    bool vec;
+};
+
+enum KernelId {
+    KID_SQ_PARTIALS = 0,
+    KID_SQ_FINALIZE,
+    KID_SUMSQ,
+    KID_S_FINALIZE,
+    KID_MOMENT,
+    KID_RES_FINALIZE,
+    KID_APPLY,
+    KID_FACTORS,
+    KID_APPLY_FLAT,
+    KID_NF_PARTIAL,
+    KID_NF_APPLY,
+    KID_COUNT
+};
+
+cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
+                            cudaStream_t st);
+cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
+                               cudaStream_t st);
+
+cudaError_t launch_quantize_blockwise(const float* src, void* q, float* absmax, int64_t n, bool is_signed,
+                                      cudaStream_t st);
+cudaError_t launch_dequantize_blockwise(const void* q, const float* absmax, float* dst, int64_t n, bool is_signed,
+                                        cudaStream_t st);
+cudaError_t launch_quantize_tile16(const float* src, int8_t* q, float* absmax, int64_t rows, int64_t cols,
+                                   cudaStream_t st);
+cudaError_t launch_dequantize_tile16(const int8_t* q, const float* absmax, float* dst, int64_t rows, int64_t cols,
+                                     cudaStream_t st);
+
+}  // namespace came

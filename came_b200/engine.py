@@ -1,0 +1,192 @@
+"""Host side of the step: turns optimizer state into the device-resident tensor table ("plan") of
+libcame_b200 and issues one C call per step per device.
+
+This is the replacement of the reference's extension shim (came_pytorch/came_cuda/__init__.py:131-1106,
+25 keyword wrappers, one pybind call per tensor per kernel group).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import CameHyper, CameTensorDesc
+
+_DT = {torch.float32: _lib.DT_F32, torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise RuntimeError(f"came_b200 supports float32/float16/bfloat16 tensors, got {dt}") from None
+
+
+@dataclass
+class Entry:
+    """One tensor of a step: the parameter/gradient views handed to the kernels and its state tensors."""
+    p: torch.Tensor
+    g: torch.Tensor
+    mode: int
+    flags: int
+    group: int                      # index into the hyper array of the step
+    m: torch.Tensor = None
+    m_absmax: torch.Tensor = None
+    sq_row: torch.Tensor = None
+    sq_row_absmax: torch.Tensor = None
+    sq_col: torch.Tensor = None
+    sq_col_absmax: torch.Tensor = None
+    res_row: torch.Tensor = None
+    res_row_absmax: torch.Tensor = None
+    res_col: torch.Tensor = None
+    res_col_absmax: torch.Tensor = None
+    keep: list = field(default_factory=list)   # temporaries that must outlive the step's kernels
+
+    def structure_key(self):
+        """Everything except the p / g addresses: a change here needs a new plan."""
+        return (tuple(self.p.shape), self.p.dtype, self.g.dtype, self.mode, self.flags, self.group,
+                self.m.data_ptr(), self.sq_row.data_ptr())
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def make_hyper(lr, betas, eps, clip_threshold, weight_decay, *, python_scalars: bool) -> CameHyper:
+    """fp32 hyper-parameters of one param_group.
+
+    python_scalars=False: 1-beta, lr*wd and 1-lr*wd are formed in fp32 from the fp32-rounded inputs, as the
+    reference kernels do after the double->float casts of came_kernels.cu:6224-6231.
+    python_scalars=True: formed in double and rounded once, as torch does for `alpha=1.0 - beta` and
+    `alpha=-weight_decay * lr` on the reference's Python paths (CAME.py:122-172, CAMECUDA.py:262-273)."""
+    f = np.float32
+    b = [f(x) for x in betas]
+    h = CameHyper()
+    h.lr = f(lr)
+    h.beta1, h.beta2, h.beta3 = b
+    if python_scalars:
+        h.om_beta1, h.om_beta2, h.om_beta3 = (f(1.0 - float(x)) for x in betas)
+        h.wd_lr = f(float(weight_decay) * float(lr))
+        h.decay_mul = f(1.0 - float(lr) * float(weight_decay))
+    else:
+        h.om_beta1, h.om_beta2, h.om_beta3 = (f(1.0) - x for x in b)
+        h.wd_lr = f(weight_decay) * f(lr)
+        h.decay_mul = f(1.0) - f(lr) * f(weight_decay)
+    h.eps0, h.eps1 = f(eps[0]), f(eps[1])
+    h.clip_threshold = f(clip_threshold)
+    h.weight_decay = f(weight_decay)
+    return h
+
+
+class DevicePlan:
+    """A came_plan_t and the workspace it lives in, for the tensors of one device."""
+
+    def __init__(self, device: torch.device, entries: list):
+        self.lib = _lib.load()
+        self.device = device
+        self.n = len(entries)
+        self.structure = tuple(e.structure_key() for e in entries)
+        self.addresses = tuple((e.p.data_ptr(), e.g.data_ptr()) for e in entries)
+        descs = (CameTensorDesc * self.n)()
+        for d, e in zip(descs, entries):
+            if e.p.dim() not in (1, 2):
+                raise NotImplementedError("came_b200 steps 1-D and 2-D tensors")
+            d.p, d.g = e.p.data_ptr(), e.g.data_ptr()
+            d.m, d.m_absmax = _ptr(e.m), _ptr(e.m_absmax)
+            d.sq_row, d.sq_row_absmax = _ptr(e.sq_row), _ptr(e.sq_row_absmax)
+            d.sq_col, d.sq_col_absmax = _ptr(e.sq_col), _ptr(e.sq_col_absmax)
+            d.res_row, d.res_row_absmax = _ptr(e.res_row), _ptr(e.res_row_absmax)
+            d.res_col, d.res_col_absmax = _ptr(e.res_col), _ptr(e.res_col_absmax)
+            d.rows = e.p.shape[0]
+            d.cols = e.p.shape[1] if e.p.dim() == 2 else 0
+            d.mode, d.flags, d.group = e.mode, e.flags, e.group
+            d.p_dtype, d.g_dtype = dtype_code(e.p.dtype), dtype_code(e.g.dtype)
+        nbytes = self.lib.came_b200_workspace_bytes(descs, self.n)
+        if nbytes == 0:
+            _lib.check(_lib.E_INVALID)
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.workspace_bytes = nbytes
+        handle = C.c_void_p()
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            _lib.check(self.lib.came_b200_plan_create(descs, self.n, self.workspace.data_ptr(), nbytes, stream,
+                                                      C.byref(handle)))
+        self.handle = handle
+
+    def repoint(self, entries: list) -> bool:
+        """Refresh p / g addresses in place; False when the library asks for a new plan instead."""
+        addresses = tuple((e.p.data_ptr(), e.g.data_ptr()) for e in entries)
+        if addresses == self.addresses:
+            return True
+        g = (C.c_void_p * self.n)(*[a[1] for a in addresses])
+        p = (C.c_void_p * self.n)(*[a[0] for a in addresses])
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            rc = self.lib.came_b200_plan_set_pointers(self.handle, g, p, self.n, stream)
+        if rc == _lib.E_INVALID:
+            return False
+        _lib.check(rc)
+        self.addresses = addresses
+        return True
+
+    def step(self, hypers: list) -> None:
+        arr = (CameHyper * len(hypers))(*hypers)
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            _lib.check(self.lib.came_b200_step(self.handle, arr, len(hypers), stream))
+
+    @property
+    def last_launches(self) -> int:
+        return self.lib.came_b200_plan_last_launches(self.handle)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.came_b200_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class StepEngine:
+    """Keeps one DevicePlan per device alive across steps and rebuilds it only when the set of
+    tensors, their state buffers or their alignment class changes."""
+
+    def __init__(self):
+        self.plans: dict = {}
+
+    def invalidate(self) -> None:
+        for plan in self.plans.values():
+            plan.close()
+        self.plans.clear()
+
+    def prepare(self, entries: list) -> list:
+        by_dev: dict = {}
+        for e in entries:
+            by_dev.setdefault(e.p.device, []).append(e)
+        ready = []
+        for dev, es in by_dev.items():
+            plan = self.plans.get(dev)
+            structure = tuple(e.structure_key() for e in es)
+            if plan is None or plan.structure != structure or not plan.repoint(es):
+                if plan is not None:
+                    plan.close()
+                plan = DevicePlan(dev, es)
+                self.plans[dev] = plan
+            ready.append(plan)
+        for dev in [d for d in self.plans if d not in by_dev]:
+            self.plans.pop(dev).close()
+        return ready
+
+    def step(self, entries: list, hypers: list) -> int:
+        launches = 0
+        for plan in self.prepare(entries):
+            plan.step(hypers)
+            launches += plan.last_launches
+        return launches
