@@ -1,6 +1,6 @@
 """Builds libcame_b200.so in-tree with nvcc for sm_100a (no JIT cache, no torch extension machinery).
 
-    python -m came_b200._build [--force] [--verbose]
+    python came_b200/_build.py [--force] [--verbose]
 """
 from __future__ import annotations
 

@@ -25,6 +25,7 @@ F_UPDATE_F16 = 1 << 7
 F_RSQRT_CLAMP = 1 << 8
 
 MAX_GROUPS = 64
+KERNEL_COUNT = 11
 OK, E_INVALID, E_WORKSPACE, E_CUDA, E_UNSUPPORTED = 0, -1, -2, -3, -4
 
 
@@ -71,6 +72,9 @@ SYMBOLS = {
                                                C.c_void_p]),
     "came_b200_step": (C.c_int, [C.c_void_p, C.POINTER(CameHyper), C.c_int, C.c_void_p]),
     "came_b200_plan_last_launches": (C.c_int, [C.c_void_p]),
+    "came_b200_plan_set_timing": (C.c_int, [C.c_void_p, C.c_int]),
+    "came_b200_plan_read_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "came_b200_kernel_name": (C.c_char_p, [C.c_int]),
 }
 
 _lib = None
@@ -83,7 +87,7 @@ def load() -> C.CDLL:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m came_b200._build` (needs nvcc, sm_100a). "
+            f"{LIB_PATH} is missing: build it with `python came_b200/_build.py` (needs nvcc, sm_100a). "
             "came_b200 has no fallback path."
         )
     lib = C.CDLL(LIB_PATH)

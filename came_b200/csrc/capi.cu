@@ -183,6 +183,12 @@ struct came_plan {
     Layout L{};
     std::vector<LaunchItem> launches;
     int last_launches = 0;
+    bool timing = false;
+    struct Timed { int kernel; cudaEvent_t t0, t1; };
+    std::vector<Timed> timed;
+    ~came_plan() {
+        for (auto& t : timed) { cudaEventDestroy(t.t0); cudaEventDestroy(t.t1); }
+    }
 };
 
 extern "C" {
@@ -360,9 +366,19 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     const Work* wbase = reinterpret_cast<const Work*>(plan->ws + plan->L.off_work);
     int launches = 0;
     for (const LaunchItem& it : plan->launches) {
+        came_plan::Timed tm{it.kernel, nullptr, nullptr};
+        if (plan->timing) {
+            if (cudaEventCreate(&tm.t0) != cudaSuccess || cudaEventCreate(&tm.t1) != cudaSuccess)
+                return fail(CAME_E_CUDA, "step: cudaEventCreate failed");
+            cudaEventRecord(tm.t0, st);
+        }
         e = (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY)
                 ? launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st)
                 : launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
+        if (plan->timing) {
+            cudaEventRecord(tm.t1, st);
+            plan->timed.push_back(tm);
+        }
         if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: kernel %d: %s", it.kernel, cudaGetErrorString(e));
         ++launches;
     }
@@ -371,5 +387,36 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
 }
 
 int came_b200_plan_last_launches(const came_plan_t* plan) { return plan ? plan->last_launches : 0; }
+
+int came_b200_plan_set_timing(came_plan_t* plan, int enable) {
+    if (!plan) return fail(CAME_E_INVALID, "set_timing: plan is null");
+    plan->timing = enable != 0;
+    return CAME_OK;
+}
+
+int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches) {
+    if (!plan || !ms || !launches) return fail(CAME_E_INVALID, "read_timing: null argument");
+    static_assert(CAME_KERNEL_COUNT == KID_COUNT, "header and kernel table out of sync");
+    for (int k = 0; k < CAME_KERNEL_COUNT; ++k) { ms[k] = 0.0f; launches[k] = 0; }
+    int rc = CAME_OK;
+    for (auto& t : plan->timed) {
+        float dt = 0.0f;
+        cudaError_t e = cudaEventSynchronize(t.t1);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&dt, t.t0, t.t1);
+        if (e == cudaSuccess) { ms[t.kernel] += dt; launches[t.kernel] += 1; }
+        else rc = fail(CAME_E_CUDA, "read_timing: %s", cudaGetErrorString(e));
+        cudaEventDestroy(t.t0);
+        cudaEventDestroy(t.t1);
+    }
+    plan->timed.clear();
+    return rc;
+}
+
+const char* came_b200_kernel_name(int kernel) {
+    static const char* names[CAME_KERNEL_COUNT] = {
+        "sq_partials", "sq_finalize", "sumsq", "s_finalize", "moment", "res_finalize",
+        "apply", "factors", "apply_flat", "nf_partial", "nf_apply"};
+    return (kernel >= 0 && kernel < CAME_KERNEL_COUNT) ? names[kernel] : "?";
+}
 
 }  // extern "C"

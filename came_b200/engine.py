@@ -142,6 +142,17 @@ class DevicePlan:
     def last_launches(self) -> int:
         return self.lib.came_b200_plan_last_launches(self.handle)
 
+    def set_timing(self, enable: bool) -> None:
+        _lib.check(self.lib.came_b200_plan_set_timing(self.handle, int(enable)))
+
+    def read_timing(self) -> dict:
+        """{kernel name: (total ms, launches)} since the last read; waits for the recorded events."""
+        ms = (C.c_float * _lib.KERNEL_COUNT)()
+        n = (C.c_int * _lib.KERNEL_COUNT)()
+        _lib.check(self.lib.came_b200_plan_read_timing(self.handle, ms, n))
+        return {self.lib.came_b200_kernel_name(k).decode(): (float(ms[k]), int(n[k]))
+                for k in range(_lib.KERNEL_COUNT) if n[k] > 0}
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.lib.came_b200_plan_destroy(self.handle)

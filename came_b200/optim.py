@@ -18,6 +18,7 @@ scratch tensor in the optimizer state and no CPU / eager fallback: parameters mu
 """
 from __future__ import annotations
 
+import copy
 import math
 import warnings
 
@@ -307,6 +308,8 @@ class _CameB200Optimizer(torch.optim.Optimizer):
                     st.pop(k, None)
                 elif torch.is_tensor(v):
                     st[k] = v.detach().to(device=p.device).clone()
+                else:
+                    st[k] = copy.deepcopy(v)   # torch's loader turns str values such as "_mode" into garbage
             if st.get("_mode") == "full8bit" and st.get("factored", False) and "factored_row_q" in st:
                 bind_flat_views(st)
         self._engine.invalidate()

@@ -153,6 +153,18 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
 /* Number of kernel launches the last came_b200_step on this plan enqueued. */
 int came_b200_plan_last_launches(const came_plan_t* plan);
 
+/*
+ * Per-kernel device timing with CUDA events recorded on the step's stream around every launch: the
+ * device-side counterpart of the reference's opt-in wall-clock dispatch counters
+ * (`_benchmark_dispatch_timing`, came_pytorch/CAME8bit.py:695-710, 898-910).  Off by default.
+ * read_timing waits for the recorded events, adds their durations into ms[k] / launches[k]
+ * (arrays of CAME_KERNEL_COUNT, zeroed by the callee) and forgets them.
+ */
+#define CAME_KERNEL_COUNT 11
+int came_b200_plan_set_timing(came_plan_t* plan, int enable);
+int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches);
+const char* came_b200_kernel_name(int kernel);
+
 /* error codes */
 #define CAME_OK 0
 #define CAME_E_INVALID (-1)   /* bad argument / descriptor; see came_b200_last_error() */

@@ -51,7 +51,10 @@ def run_pair(opt_cls, preset_of, shapes, dtype, steps, hyper, seed, device="cuda
     cp = [p.clone() for p in params0]
     sems = [preset_of(p.dim()) for p in cp]
     states = [orc.init_state(p, s) for p, s in zip(cp, sems)]
-    out = {"p_rel": 0.0, "p_ulp_frac": 0.0, "p_maxulp": 0.0, "code_frac": 0.0, "code_max": 0, "f_rel": 0.0}
+    out = {"p_rel": 0.0, "p_diff_frac": 0.0, "p_maxspacing": 0.0, "p_far_frac": 0.0, "code_frac": 0.0, "code_frac2": 0.0, "code_max": 0,
+           "f_rel": 0.0}
+    eps = {torch.float32: 2.0 ** -23, torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10}[dtype]
+    scale = [p.float().abs() for p in cp]      # running max of |p| per entry: the magnitude a rounding happened at
     for gs in grads:
         for p, g in zip(gp, gs):
             p.grad = g.clone().to(device)
@@ -59,21 +62,24 @@ def run_pair(opt_cls, preset_of, shapes, dtype, steps, hyper, seed, device="cuda
         for i, g in enumerate(gs):
             kw = (oracle_kw or {}) if cp[i].dim() == 1 else {}
             cp[i] = orc.step(cp[i], g, states[i], hp, sems[i], **kw)
-        for p, c in zip(gp, cp):
+        for i, (p, c) in enumerate(zip(gp, cp)):
             got, ref = p.data.float().cpu(), c.float()
+            scale[i] = torch.maximum(scale[i], ref.abs())
             out["p_rel"] = max(out["p_rel"], relerr(got, ref))
-            if dtype != torch.float32:
-                eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
-                ulp = (ref.abs() * eps * 2).clamp_min(1e-30)
-                d = (got - ref).abs() / ulp
-                out["p_ulp_frac"] = max(out["p_ulp_frac"], (got != ref).float().mean().item())
-                out["p_maxulp"] = max(out["p_maxulp"], d.max().item())
+            # distance in spacings of `dtype` at the running-max magnitude, with a tenth of a typical update
+            # (lr * 1) as floor: an entry that cancels to ~0 has no meaningful spacing of its own
+            spacing = (scale[i] * eps).clamp_min(0.1 * hyper["lr"])
+            out["p_diff_frac"] = max(out["p_diff_frac"], (got != ref).float().mean().item())
+            dist = (got - ref).abs() / spacing
+            out["p_maxspacing"] = max(out["p_maxspacing"], dist.max().item())
+            out["p_far_frac"] = max(out["p_far_frac"], (dist > 2.0).float().mean().item())
     for p, st in zip(gp, states):
         gst = opt.state[p]
         for k in STATE_KEYS_Q:
             if k in st:
                 d = (gst[k].cpu().to(torch.int32) - st[k].to(torch.int32)).abs()
                 out["code_frac"] = max(out["code_frac"], (d != 0).float().mean().item())
+                out["code_frac2"] = max(out["code_frac2"], (d > 1).float().mean().item())
                 out["code_max"] = max(out["code_max"], int(d.max().item()))
         for k in STATE_KEYS_F:
             if k in st:

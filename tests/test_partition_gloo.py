@@ -1,0 +1,83 @@
+"""Ownership partition + flat-buffer all-gather on CPU ranks (gloo, world_size 2): the owners form a
+partition, views alias the flat buffer, and after step + all-gather every rank holds the same weights as a
+single process stepping everything.  The step itself is played by the CPU oracle (the CUDA kernels need a
+GPU); what is under test is the host-side sharding logic."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from came_b200.partition import ShardedParams, assign_owners, imbalance
+
+SHAPES = [(64, 48), (300,), (33, 17), (128, 256), (40,), (96, 64), (16, 16)]
+
+
+def test_assign_owners_is_a_balanced_partition():
+    numels = [4096 * 4096] * 128 + [4096 * 11008] * 96 + [32000 * 4096] * 2 + [4096] * 65
+    for w in (1, 2, 4, 8):
+        owners = assign_owners(numels, w)
+        assert len(owners) == len(numels) and set(owners) <= set(range(w))
+        assert imbalance(numels, owners, w) < 1.02
+    assert assign_owners([5, 5, 5], 2) == assign_owners([5, 5, 5], 2)      # deterministic
+    with pytest.raises(ValueError):
+        assign_owners([1], 0)
+
+
+def test_views_alias_flat_buffer_and_are_aligned():
+    sp = ShardedParams(SHAPES, torch.bfloat16, "cpu", world_size=2, rank=1)
+    assert sp.flat.numel() == 2 * sp.slice_len
+    seen = torch.zeros(sp.flat.numel(), dtype=torch.int32)
+    for v, r in zip(sp.views, sp.owners):
+        off = (v.data_ptr() - sp.flat.data_ptr()) // 2
+        assert off % 128 == 0 and r * sp.slice_len <= off < (r + 1) * sp.slice_len
+        seen[off:off + v.numel()] += 1
+    assert int(seen.max()) == 1
+    sp.views[0].fill_(3.0)
+    assert float(sp.flat.float().sum()) == 3.0 * sp.views[0].numel()
+    assert sorted(sp.owned) == [i for i, r in enumerate(sp.owners) if r == 1]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import came_oracle as orc
+        torch.manual_seed(0)
+        init = [torch.randn(s) * 0.02 for s in SHAPES]
+        grads = [torch.randn(s) * 1e-3 for s in SHAPES]
+        sp = ShardedParams(SHAPES, torch.float32, "cpu", world, rank)
+        for v, x in zip(sp.views, init):
+            v.copy_(x)
+        hp = orc.Hyper(weight_decay=1e-2)
+        for i in sp.owned:                      # each rank steps only the tensors it owns
+            st = orc.init_state(sp.views[i], orc.CUDAFP)
+            sp.views[i].copy_(orc.step(sp.views[i].clone(), grads[i], st, hp, orc.CUDAFP))
+        sp.all_gather()
+        torch.save([v.clone() for v in sp.views], os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_step_then_all_gather_matches_single_process(tmp_path):
+    from oracle import came_oracle as orc
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    torch.manual_seed(0)
+    init = [torch.randn(s) * 0.02 for s in SHAPES]
+    grads = [torch.randn(s) * 1e-3 for s in SHAPES]
+    hp = orc.Hyper(weight_decay=1e-2)
+    want = [orc.step(p.clone(), g, orc.init_state(p, orc.CUDAFP), hp, orc.CUDAFP) for p, g in zip(init, grads)]
+    got = [torch.load(os.path.join(str(tmp_path), f"rank{r}.pt")) for r in range(world)]
+    for r in range(world):
+        for a, b in zip(got[r], want):
+            assert torch.equal(a, b)
