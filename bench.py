@@ -53,10 +53,19 @@ def llama7b_shapes():
     return shapes
 
 
+def profile_shapes():
+    """A small case of the same kernels for profiler captures: a few matrices of the Llama-7B shapes
+    (0.24 G elements, 2 GB on the device; gradients alone are 4x the L2)."""
+    return [(4096, 11008)] * 2 + [(11008, 4096)] * 2 + [(4096, 4096)] * 4 + [(4096,)] * 2
+
+
 def cpu_sample_shapes():
     """The bounded sample of the same workload that the CPU legs step: one tensor of each distinct matrix
     shape inside a layer plus one norm vector (107 M elements)."""
     return [(4096, 4096), (4096, 11008), (11008, 4096), (4096,)]
+
+
+WORKLOADS = {"llama7b": llama7b_shapes, "profile": profile_shapes}
 
 
 def peaks():
@@ -198,7 +207,7 @@ def run_gpu(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    shapes = llama7b_shapes()
+    shapes = WORKLOADS[args.workload]()
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
     sp = ShardedParams(shapes, torch.bfloat16, dev, world, rank)
@@ -314,7 +323,7 @@ def run_gpu(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded; same gradient "
             "tensors every step; 54 GB touched per step, far above the 126 MB L2)",
-            "config": {"workload": "llama7b_came8bit_bf16", "tensors": len(shapes), "elements": total_elems,
+            "config": {"workload": args.workload + "_came8bit_bf16", "tensors": len(shapes), "elements": total_elems,
                        "state": "int8 exp_avg per 16x16 tile + uint8 row/col vectors (CAME8bit)",
                        "parallelism": f"ownership x{world} + all-gather" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2"},
@@ -351,6 +360,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="llama7b", choices=["llama7b", "profile"],
+                    help="llama7b: the benchmark workload; profile: a small case of the same kernels for ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

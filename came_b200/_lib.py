@@ -72,6 +72,7 @@ SYMBOLS = {
                                                C.c_void_p]),
     "came_b200_step": (C.c_int, [C.c_void_p, C.POINTER(CameHyper), C.c_int, C.c_void_p]),
     "came_b200_plan_last_launches": (C.c_int, [C.c_void_p]),
+    "came_b200_plan_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "came_b200_plan_set_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "came_b200_plan_read_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "came_b200_kernel_name": (C.c_char_p, [C.c_int]),

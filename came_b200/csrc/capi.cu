@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <new>
@@ -19,6 +20,9 @@ constexpr int MAX_GROUPS = 64;
 constexpr size_t ALIGN = 256;
 
 thread_local char g_err[512] = "";
+// CAME_B200_DISABLE_FAST=1 in the environment routes every tensor through the generic kernels (used by the
+// tests to compare the two implementations of a pass against each other)
+const bool g_disable_fast = [] { const char* e = getenv("CAME_B200_DISABLE_FAST"); return e && e[0] == '1'; }();
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -37,24 +41,31 @@ struct LaunchItem {
     KernelKey key;
     size_t work_off;   // in Work units from the start of the work region
     int n;
+    size_t extra;      // fused first pass: largest staged slot (bytes) among the tensors of the launch
 };
+
+inline int elem_bytes(int dt) { return dt == CAME_DT_F32 ? 4 : 2; }
 
 // vector-path eligibility of a tensor for each kernel family
 struct VecFlags {
-    bool k;      // gradient reductions: runs of 8
-    bool p2;     // momentum pass: runs of 16 over g and m
-    bool p3;     // apply pass: runs of 16 over m and p
-    bool flat;   // flat apply: runs of 8 over g, m, p
+    int k;      // gradient reductions: 1 = runs of 8
+    int p2;     // momentum pass: 1 = runs of 16 over g and m, 2 = staged fast path (tile layout, cols % 256 == 0)
+    int p3;     // apply pass: same over m and p
+    int flat;   // flat apply: 1 = runs of 8 over g, m, p
     bool operator==(const VecFlags& o) const { return k == o.k && p2 == o.p2 && p3 == o.p3 && flat == o.flat; }
 };
 
 VecFlags vec_flags(const CameTensorDesc& d) {
-    VecFlags v{false, false, false, false};
+    VecFlags v{0, 0, 0, 0};
     if (d.cols == 0) return v;
     const bool c8 = d.cols % 8 == 0, c16 = d.cols % 16 == 0;
+    // staged fast path of the momentum / apply passes: both or neither, as they share the tile geometry
+    const bool fast = d.mode == CAME_MODE_TILE8 && d.cols % 64 == 0 && !g_disable_fast && aligned16(d.g) &&
+                      aligned16(d.m) && aligned16(d.p);
     v.k = c8 && aligned16(d.g);
-    v.p2 = c16 && aligned16(d.g) && aligned16(d.m);
-    v.p3 = c16 && aligned16(d.p) && aligned16(d.m);
+    if (v.k && !g_disable_fast && !(d.flags & CAME_F_SQ_CLAMP) && fused_sq_eligible(d.cols, elem_bytes(d.g_dtype))) v.k = 2;
+    v.p2 = (c16 && aligned16(d.g) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
+    v.p3 = (c16 && aligned16(d.p) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.flat = c8 && aligned16(d.g) && aligned16(d.p) && (reinterpret_cast<uintptr_t>(d.m) & 7u) == 0;
     return v;
 }
@@ -78,8 +89,9 @@ Geometry geometry(const CameTensorDesc& d) {
     g.nbC = (int)cdiv(g.C, QBLOCK);
     g.tiles_r = (int)cdiv(g.R, K_TR);
     g.tiles_c = (int)cdiv(g.C, K_TC);
-    g.ptiles_r = (int)cdiv(g.R, P_TR);
-    g.ptiles_c = (int)cdiv(g.C, P_TC);
+    const bool wide = vec_flags(d).p2 == 2;
+    g.ptiles_r = (int)cdiv(g.R, wide ? W_TR : P_TR);
+    g.ptiles_c = (int)cdiv(g.C, wide ? W_TC : P_TC);
     g.flat_chunks = cdiv(cdiv(g.R * g.C, QBLOCK), FLAT_BLOCKS_PER_CTA);
     return g;
 }
@@ -106,8 +118,13 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.scal = take(4);
         s.rowpart = take((size_t)std::max(g.tiles_c, g.ptiles_c) * (size_t)g.R);
         s.colpart = take((size_t)std::max(g.tiles_r, g.ptiles_r) * (size_t)g.C);
-        s.spart = take((size_t)g.tiles_r * (size_t)g.tiles_c);
+        s.spart = take(std::max((size_t)g.tiles_r * (size_t)g.tiles_c, (size_t)g.nbC));
         s.fac = d.mode == CAME_MODE_FLAT8 ? take(2 * (size_t)(g.R + g.C)) : nullptr;
+        if (vec_flags(d).k == 2) {
+            s.fused_a = 1;
+            s.fa_rb = fused_sq_rows_per_batch(g.C * elem_bytes(d.g_dtype));
+            s.tpart = take((size_t)g.tiles_r * (size_t)g.C);
+        }
     }
     if (out) *out = s;
     return off;
@@ -135,7 +152,7 @@ int validate(const CameTensorDesc& d, int i) {
 }
 
 struct Layout {
-    size_t off_descs, off_scr, off_hyp, off_work, off_float, total;
+    size_t off_descs, off_scr, off_hyp, off_status, off_work, off_float, total;
     size_t n_work;
 };
 
@@ -163,6 +180,7 @@ Layout layout(const CameTensorDesc* descs, int n) {
     L.off_descs = off; off = align_up(off + (size_t)n * sizeof(CameTensorDesc));
     L.off_scr = off;   off = align_up(off + (size_t)n * sizeof(Scratch));
     L.off_hyp = off;   off = align_up(off + (size_t)MAX_GROUPS * sizeof(CameHyper));
+    L.off_status = off; off = align_up(off + sizeof(int));
     L.n_work = count_work(descs, n);
     L.off_work = off;  off = align_up(off + L.n_work * sizeof(Work));
     L.off_float = off;
@@ -271,7 +289,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
         for (auto& kv : groups) {
             LaunchItem it{};
             it.kernel = kernel;
-            it.key = KernelKey{std::get<0>(kv.first), std::get<1>(kv.first), std::get<2>(kv.first), std::get<3>(kv.first) != 0};
+            it.key = KernelKey{std::get<0>(kv.first), std::get<1>(kv.first), std::get<2>(kv.first), std::get<3>(kv.first)};
             it.work_off = work.size();
             for (int i : kv.second) {
                 const int64_t c = count(i);
@@ -291,10 +309,20 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
 
     build(KID_NF_PARTIAL, is1d, [&](int i) { return Key{D[i].g_dtype, 0, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
     build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
-    build(KID_SQ_PARTIALS, is2d, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
+    auto fusedA = [&](int i) { return D[i].cols != 0 && vf[i].k == 2; };
+    auto twopass = [&](int i) { return D[i].cols != 0 && vf[i].k != 2; };
+    auto groups_per_thread = [&](int i) { return (int)cdiv(cdiv(D[i].cols, 8), 512); };
+    build(KID_SQ_PARTIALS, fusedA, [&](int i) { return Key{D[i].g_dtype, 0, groups_per_thread(i), 2}; },
+          [&](int i) { return (int64_t)geo[i].tiles_r; });
+    for (auto& it : plan->launches)   // slot size of each fused launch = the largest among its tensors
+        if (it.kernel == KID_SQ_PARTIALS)
+            for (int i = 0; i < n_tensors; ++i)
+                if (fusedA(i) && D[i].g_dtype == it.key.g_dtype && groups_per_thread(i) == it.key.mode)
+                    it.extra = std::max(it.extra, (size_t)scr[i].fa_rb * (size_t)D[i].cols * elem_bytes(D[i].g_dtype));
+    build(KID_SQ_PARTIALS, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
-    build(KID_SUMSQ, is2d, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
+    build(KID_SUMSQ, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     build(KID_S_FINALIZE, is2d, nokey, [&](int) { return (int64_t)1; });
     build(KID_MOMENT, is2d, [&](int i) { return Key{D[i].g_dtype, 0, D[i].mode, vf[i].p2}; },
@@ -316,6 +344,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
                                     cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(plan->ws + L.off_scr, scr.data(), (size_t)n_tensors * sizeof(Scratch), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(plan->ws + L.off_status, 0, sizeof(int), st);
     if (e == cudaSuccess && !work.empty())
         e = cudaMemcpyAsync(plan->ws + L.off_work, work.data(), work.size() * sizeof(Work), cudaMemcpyHostToDevice, st);
     // the host vectors above die at return: wait for the copies
@@ -362,7 +391,8 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: hyper-parameter upload: %s", cudaGetErrorString(e));
     StepArgs a{reinterpret_cast<const CameTensorDesc*>(plan->ws + plan->L.off_descs),
                reinterpret_cast<const Scratch*>(plan->ws + plan->L.off_scr),
-               reinterpret_cast<const CameHyper*>(plan->ws + plan->L.off_hyp)};
+               reinterpret_cast<const CameHyper*>(plan->ws + plan->L.off_hyp),
+               reinterpret_cast<int*>(plan->ws + plan->L.off_status)};
     const Work* wbase = reinterpret_cast<const Work*>(plan->ws + plan->L.off_work);
     int launches = 0;
     for (const LaunchItem& it : plan->launches) {
@@ -372,9 +402,12 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
                 return fail(CAME_E_CUDA, "step: cudaEventCreate failed");
             cudaEventRecord(tm.t0, st);
         }
-        e = (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY)
-                ? launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st)
-                : launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
+        if (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY)
+            e = launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
+        else if (it.kernel == KID_SQ_PARTIALS && it.key.variant == 2)
+            e = launch_fused_sq(it.key, a, wbase + it.work_off, it.n, it.extra, st);
+        else
+            e = launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         if (plan->timing) {
             cudaEventRecord(tm.t1, st);
             plan->timed.push_back(tm);
@@ -387,6 +420,14 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
 }
 
 int came_b200_plan_last_launches(const came_plan_t* plan) { return plan ? plan->last_launches : 0; }
+
+int came_b200_plan_status(came_plan_t* plan, came_stream_t stream, int* status) {
+    if (!plan || !status) return fail(CAME_E_INVALID, "plan_status: null argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(status, plan->ws + plan->L.off_status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "plan_status: %s", cudaGetErrorString(e));
+}
 
 int came_b200_plan_set_timing(came_plan_t* plan, int enable) {
     if (!plan) return fail(CAME_E_INVALID, "set_timing: plan is null");

@@ -22,6 +22,10 @@ constexpr int K_TC = 512;
 constexpr int P_TR = 128;
 constexpr int P_TC = 256;
 constexpr int THREADS = 256;
+// tile of the shared-memory staged (tile-layout) momentum / apply passes
+constexpr int W_TR = 128;
+constexpr int W_TC = 1024;
+constexpr int W_THREADS = 512;
 // flat blocks (of 256 elements) handled by one CTA of the flat-layout apply pass
 constexpr int FLAT_BLOCKS_PER_CTA = 64;
 
@@ -39,9 +43,12 @@ struct Scratch {
     float* colpart;   // [tiles_r * cols]                 per-CTA column partial sums
     float* spart;     // [tiles_r * tiles_c] partials of S; 1-D tensors: [nbR] block partials of sum u^2
     float* fac;       // flat layout only: r[rows], c[cols], R'[rows], C'[cols] factors, else nullptr
+    float* tpart;     // fused first pass only: [tiles_r * cols] per-strip column sums of g^2 / v_row
     int32_t tiles_r, tiles_c;     // K_TR x K_TC grid
-    int32_t ptiles_r, ptiles_c;   // P_TR x P_TC grid
+    int32_t ptiles_r, ptiles_c;   // P_TR x P_TC grid (W_TR x W_TC when the staged fast path runs)
     int32_t nbR, nbC;             // ceil(rows/256), ceil(cols/256)
+    int32_t fused_a;              // 1: the fused first pass runs (complete row sums, v_row and tpart come from it)
+    int32_t fa_rb;                // fused first pass: rows per staged batch
 };
 
 struct Work {

@@ -123,26 +123,36 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
     float* absmax = RES ? (is_col ? d.res_col_absmax : d.res_row_absmax) : (is_col ? d.sq_col_absmax : d.sq_row_absmax);
     float* fresh = RES ? (is_col ? s.Rc : s.Rr) : (is_col ? s.vc : s.vr);
 
-    float v = 0.0f;
+    // the fused first pass delivers finished v_row values, column sums without eps0, and tpart
+    const bool fused = !RES && s.fused_a;
+    float v = 0.0f, tsum = 0.0f;
     if (valid) {
-        float acc = 0.0f;
-        if (!is_col) {
-            const int parts = RES ? s.ptiles_c : s.tiles_c;
-            for (int t = 0; t < parts; ++t) acc += s.rowpart[(int64_t)t * R + idx];
-            acc = acc / (float)C;
+        if (fused && !is_col) {
+            v = s.vr[idx];
         } else {
-            const int parts = RES ? s.ptiles_r : s.tiles_r;
-            for (int t = 0; t < parts; ++t) acc += s.colpart[(int64_t)t * C + idx];
-            acc = acc / (float)R;
+            float acc = 0.0f;
+            if (!is_col) {
+                const int parts = RES ? s.ptiles_c : s.tiles_c;
+                for (int t = 0; t < parts; ++t) acc += s.rowpart[(int64_t)t * R + idx];
+                acc = acc / (float)C;
+            } else {
+                const int parts = RES ? s.ptiles_r : s.tiles_r;
+                for (int t = 0; t < parts; ++t) acc += s.colpart[(int64_t)t * C + idx];
+                if (fused) {
+                    acc += (float)R * h.eps0;
+                    for (int t = 0; t < parts; ++t) tsum += s.tpart[(int64_t)t * C + idx];
+                }
+                acc = acc / (float)R;
+            }
+            float old;
+            if (quant) {
+                old = (float)reinterpret_cast<const uint8_t*>(state)[idx] * (absmax[b] / QMAX_U8);
+            } else {
+                old = reinterpret_cast<const float*>(state)[idx];
+            }
+            v = old * beta + om * acc;
+            fresh[idx] = v;
         }
-        float old;
-        if (quant) {
-            old = (float)reinterpret_cast<const uint8_t*>(state)[idx] * (absmax[b] / QMAX_U8);
-        } else {
-            old = reinterpret_cast<const float*>(state)[idx];
-        }
-        v = old * beta + om * acc;
-        fresh[idx] = v;
     }
     if (quant) {
         const float bmax = fix_absmax(block_max(valid ? v : 0.0f, red));   // syncs: every old absmax read is done
@@ -154,6 +164,10 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
     if (!is_col) {
         const float bs = block_sum(valid ? v : 0.0f, red);
         if (threadIdx.x == 0) (RES ? s.rowblk2 : s.rowblk)[b] = bs;
+    } else if (fused) {
+        // this block's share of sum_j T_j / v_col_j  (S = mean(v_row) * that sum, see fused_sq.cu)
+        const float bs = block_sum((valid && v > 0.0f) ? tsum / v : 0.0f, red);
+        if (threadIdx.x == 0) s.spart[b] = bs;
     }
 }
 
@@ -213,7 +227,14 @@ __global__ void __launch_bounds__(THREADS) k_s_finalize(StepArgs a, const Work* 
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
     const Scratch& s = a.scr[w.tensor];
-    const float S = block_vector_sum(s.spart, s.tiles_r * s.tiles_c, red);
+    float S;
+    if (s.fused_a) {
+        float mean = block_vector_sum(s.rowblk, s.nbR, red) / (float)d.rows;
+        mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, d.flags & CAME_F_SQ_CLAMP);
+        S = mean * block_vector_sum(s.spart, s.nbC, red);
+    } else {
+        S = block_vector_sum(s.spart, s.tiles_r * s.tiles_c, red);
+    }
     if (threadIdx.x == 0) {
         const float n = (float)((int64_t)d.rows * d.cols);
         const float rms = sqrtf(S / n);
@@ -580,15 +601,19 @@ static KernelFn pick_apply_flat(int g, int p, bool vec) {
 cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                             cudaStream_t st) {
     switch (kernel) {
-        case KID_SQ_PARTIALS: return go(pick_sq_partials(key.g_dtype, key.vec), a, work, n, st);
+        case KID_SQ_PARTIALS: return go(pick_sq_partials(key.g_dtype, (key.variant >= 1)), a, work, n, st);
         case KID_SQ_FINALIZE: return go(k_vec_finalize<false>, a, work, n, st);
-        case KID_SUMSQ: return go(pick_sumsq(key.g_dtype, key.vec), a, work, n, st);
+        case KID_SUMSQ: return go(pick_sumsq(key.g_dtype, (key.variant >= 1)), a, work, n, st);
         case KID_S_FINALIZE: return go(k_s_finalize, a, work, n, st);
-        case KID_MOMENT: return go(pick_moment(key.g_dtype, key.mode, key.vec), a, work, n, st);
+        case KID_MOMENT:
+            if (key.variant == 2) return launch_fast_tile8(kernel, key, a, work, n, st);
+            return go(pick_moment(key.g_dtype, key.mode, (key.variant >= 1)), a, work, n, st);
         case KID_RES_FINALIZE: return go(k_vec_finalize<true>, a, work, n, st);
-        case KID_APPLY: return go(pick_apply(key.p_dtype, key.mode, key.vec), a, work, n, st);
+        case KID_APPLY:
+            if (key.variant == 2) return launch_fast_tile8(kernel, key, a, work, n, st);
+            return go(pick_apply(key.p_dtype, key.mode, (key.variant >= 1)), a, work, n, st);
         case KID_FACTORS: return go(k_factors, a, work, n, st);
-        case KID_APPLY_FLAT: return go(pick_apply_flat(key.g_dtype, key.p_dtype, key.vec), a, work, n, st);
+        case KID_APPLY_FLAT: return go(pick_apply_flat(key.g_dtype, key.p_dtype, (key.variant >= 1)), a, work, n, st);
         default: return cudaErrorInvalidValue;
     }
 }

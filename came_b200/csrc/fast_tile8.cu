@@ -1,0 +1,510 @@
+// Tile-layout (CAME8bit / CAME8bit2D) momentum and apply passes for matrices whose column count is a
+// multiple of 64 and whose buffers are 16-byte aligned.
+//
+// Persistent CTAs (one per SM, 512 threads) walk a strided share of the work list.  A work item is a tile of
+// 128 rows x up to 1024 columns, consumed in 8 bands of 16 rows.  Bands are staged in shared memory by bulk
+// asynchronous copies (TMA, one copy per row per operand: 2 KB / 1 KB, the size at which the copy engine
+// reaches full bandwidth) through a ring of mbarriers that runs ahead across item boundaries.  Arithmetic
+// uses packed fp32x2 instructions; int8 <-> fp32 conversion goes through byte permutes.
+//
+// Warp w owns columns [64w, 64w+64) of the tile (four exp_avg tiles).  Within a band a lane owns 8
+// consecutive columns (lane & 7) of 4 rows (lane >> 3, +4, +8, +12): column sums stay in 8 registers across
+// the bands, row sums need a 3-step shuffle, a 16x16 tile is shared by 8 lanes.
+//
+// Results equal those of k_moment / k_apply in factored.cu up to the order of a few fp32 roundings.
+#include "common.cuh"
+#include "launch.h"
+#include "pipeline.cuh"
+
+namespace came {
+
+constexpr int W_WARPS = W_THREADS / 32;          // 16
+constexpr int W_BAND = 16;
+constexpr int W_BANDS = W_TR / W_BAND;           // 8
+constexpr int W_MROW = W_TC + 64;                // staged row of int8 codes (+64: rows r, r+1 fall in different banks)
+
+template <typename T> struct WideCfg {
+    static constexpr int ROW = W_TC * (int)sizeof(T);                  // staged row of T
+    static constexpr int STAGE = W_BAND * (ROW + W_MROW);
+    static constexpr int STAGES = sizeof(T) == 2 ? 4 : 2;
+};
+
+// 8 consecutive staged elements -> 4 packed fp32 pairs
+__device__ __forceinline__ void wide_run8(const __nv_bfloat16* p, u64* out) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out[j] = pk_u32(w[j] << 16, w[j] & 0xffff0000u);
+}
+__device__ __forceinline__ void wide_run8(const __half* p, u64* out) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        out[j] = pk(f.x, f.y);
+    }
+}
+__device__ __forceinline__ void wide_run8(const float* p, u64* out) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    out[0] = pk(a.x, a.y); out[1] = pk(a.z, a.w); out[2] = pk(b.x, b.y); out[3] = pk(b.z, b.w);
+}
+// 8 values -> T, one or two 16-byte stores
+__device__ __forceinline__ void wide_store8(__nv_bfloat16* dst, const u64* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        upk(v[j], lo, hi);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void wide_store8(__half* dst, const u64* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        upk(v[j], lo, hi);
+        const __half2 h = __floats2half2_rn(lo, hi);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void wide_store8(float* dst, const u64* v) {
+    float a, b, c, d;
+    upk(v[0], a, b); upk(v[1], c, d);
+    reinterpret_cast<float4*>(dst)[0] = make_float4(a, b, c, d);
+    upk(v[2], a, b); upk(v[3], c, d);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(a, b, c, d);
+}
+// the value a T-typed parameter holds after a store, for a packed pair
+template <typename T> __device__ __forceinline__ u64 round_pair(u64 v);
+template <> __device__ __forceinline__ u64 round_pair<float>(u64 v) { return v; }
+template <> __device__ __forceinline__ u64 round_pair<__nv_bfloat16>(u64 v) {
+    float lo, hi;
+    upk(v, lo, hi);
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+    return pk_u32(w << 16, w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ u64 round_pair<__half>(u64 v) {
+    float lo, hi;
+    upk(v, lo, hi);
+    const float2 f = __half22float2(__floats2half2_rn(lo, hi));
+    return pk(f.x, f.y);
+}
+
+// geometry of one work item, as the producer and the consumers need it
+struct WideItem {
+    const unsigned char* a_src;   // operand A (gradient or parameter), first byte of the tile
+    const unsigned char* m_src;   // int8 codes, first byte of the tile
+    int64_t a_pitch, m_pitch;
+    int tensor, R, C, row0, col0, wcols, nbands, tr, tc;
+};
+
+template <typename TA>
+__device__ __forceinline__ WideItem wide_item(const StepArgs& a, const Work& w, bool a_is_grad) {
+    const CameTensorDesc& d = a.descs[w.tensor];
+    const Scratch& s = a.scr[w.tensor];
+    WideItem it;
+    it.tensor = w.tensor;
+    it.R = (int)d.rows;
+    it.C = (int)d.cols;
+    it.tr = w.tile / s.ptiles_c;
+    it.tc = w.tile - it.tr * s.ptiles_c;
+    it.row0 = it.tr * W_TR;
+    it.col0 = it.tc * W_TC;
+    it.wcols = min(W_TC, it.C - it.col0);
+    it.nbands = min(W_BANDS, (it.R - it.row0 + W_BAND - 1) / W_BAND);
+    it.a_pitch = (int64_t)it.C * sizeof(TA);
+    it.m_pitch = it.C;
+    it.a_src = reinterpret_cast<const unsigned char*>(a_is_grad ? d.g : d.p) + (int64_t)it.row0 * it.a_pitch +
+               (int64_t)it.col0 * sizeof(TA);
+    it.m_src = reinterpret_cast<const unsigned char*>(d.m) + (int64_t)it.row0 * it.m_pitch + it.col0;
+    return it;
+}
+
+// The producer (warp 0) walks the same item sequence as the consumers, a few bands ahead.
+template <typename TA>
+struct WideProducer {
+    int item, band, q;     // next band to issue: work-list index, band inside it, position in the band stream
+    WideItem it;
+    bool live;
+    __device__ __forceinline__ void init(const StepArgs& a, const Work* work, int n_items, bool a_is_grad) {
+        item = blockIdx.x; band = 0; q = 0;
+        live = item < n_items;
+        if (live) it = wide_item<TA>(a, work[item], a_is_grad);
+    }
+    // all 32 lanes of warp 0 call this: lane L < 16 copies row L of A, lane L >= 16 row L-16 of the codes
+    __device__ __forceinline__ void issue(const StepArgs& a, const Work* work, int n_items, bool a_is_grad,
+                                          unsigned char* smem, uint64_t* bars, int lane) {
+        if (!live) return;
+        constexpr int STAGES = WideCfg<TA>::STAGES, STAGE = WideCfg<TA>::STAGE, ROW = WideCfg<TA>::ROW;
+        const int slot = q % STAGES;
+        const int rows = min(W_BAND, it.R - it.row0 - band * W_BAND);
+        const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(TA), m_bytes = (uint32_t)it.wcols;
+        if (lane == 0) mbar_arrive_expect_tx(&bars[slot], (uint32_t)rows * (a_bytes + m_bytes));
+        __syncwarp();
+        const int r = lane & 15;
+        if (r < rows) {
+            const int64_t row = band * W_BAND + r;
+            if (lane < 16) bulk_g2s(smem + slot * STAGE + r * ROW, it.a_src + row * it.a_pitch, a_bytes, &bars[slot]);
+            else bulk_g2s(smem + slot * STAGE + W_BAND * ROW + r * W_MROW, it.m_src + row * it.m_pitch, m_bytes, &bars[slot]);
+        }
+        ++q;
+        if (++band == it.nbands) {
+            band = 0;
+            item += gridDim.x;
+            live = item < n_items;
+            if (live) it = wide_item<TA>(a, work[item], a_is_grad);
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// momentum pass (reference: kUpdateExpAvgQuantAndResSumsTiled came_kernels.cu:2584-2683)
+// ------------------------------------------------------------------------------------------------
+template <typename TG>
+__global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+    constexpr int STAGES = WideCfg<TG>::STAGES, STAGE = WideCfg<TG>::STAGE, ROW = WideCfg<TG>::ROW;
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    float* s_r = reinterpret_cast<float*>(bars + 8);
+    float* s_c = s_r + W_TR;
+    float* s_row = s_c + W_TC;                 // [W_WARPS][W_TR]
+    float* red = s_row + W_WARPS * W_TR;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c8 = lane & 7, rsub = lane >> 3;
+    const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) mbar_init(&bars[i], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    WideProducer<TG> prod;
+    if (warp == 0) {
+        prod.init(a, work, n_items, true);
+        for (int i = 0; i < STAGES - 1; ++i) prod.issue(a, work, n_items, true, smem, bars, lane);
+    }
+    const u64 c127 = splat(QMAX_I8), magic = splat(ROUND_MAGIC);
+    int q = 0;            // position of the next band to consume in this CTA's band stream
+    bool ok = true;
+
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const WideItem it = wide_item<TG>(a, work[item], true);
+        const CameTensorDesc& d = a.descs[it.tensor];
+        const Scratch& s = a.scr[it.tensor];
+        const CameHyper& h = a.hyp[d.group];
+        const int R = it.R, C = it.C;
+        const bool active = cl < it.wcols;        // warps beyond a ragged tile width idle
+        const int col = it.col0 + cl;
+        const int tile_cols = C >> 4;
+        {   // row / column factors of this tile (same arithmetic as stage_factors in factored.cu)
+            const bool clamp = d.flags & CAME_F_SQ_CLAMP;
+            float mean = block_vector_sum(s.rowblk, s.nbR, red) / (float)R;
+            mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
+            const float inv_clip = 1.0f / s.scal[1];
+            for (int i = threadIdx.x; i < W_TR; i += W_THREADS)
+                s_r[i] = (it.row0 + i < R) ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
+            for (int i = threadIdx.x; i < it.wcols; i += W_THREADS) s_c[i] = col_factor(s.vc[it.col0 + i], clamp);
+            __syncthreads();
+        }
+        u64 cf2[4], colacc[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            cf2[j] = active ? pk(s_c[cl + 2 * j], s_c[cl + 2 * j + 1]) : 0ull;
+            colacc[j] = 0ull;
+        }
+        // old tile absmax, fetched one band ahead: a dependent global load at the top of every band would sit
+        // on the critical path of the iteration
+        const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
+        float a_next = active ? amax_col[0] : 0.0f;
+        const u64 om2 = splat(h.om_beta1), eps2 = splat(h.eps1);
+        const float beta1 = h.beta1;
+
+#pragma unroll 1
+        for (int k = 0; k < it.nbands; ++k, ++q) {
+            const int slot = q % STAGES;
+            // The result of the bounded wait is made uniform over the CTA so that all warps leave together.
+            // The barrier also means every warp is done with the previous band, whose slot is refilled next.
+            if (!__syncthreads_and(mbar_wait(&bars[slot], (q / STAGES) & 1))) { ok = false; break; }
+            if (warp == 0) prod.issue(a, work, n_items, true, smem, bars, lane);
+            if (!active) continue;
+            const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(TG);
+            const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
+            const int brow = it.row0 + k * W_BAND;
+            const int64_t tile_id = (int64_t)(brow >> 4) * tile_cols + (col >> 4);
+            const float a_old = a_next;
+            if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
+            const u64 scb2 = splat(a_old > 0.0f ? (a_old / QMAX_I8) * beta1 : 0.0f);
+
+            u64 m2[4][4];
+            float rsum[4];
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = rsub + 4 * i;
+                const bool live = brow + r < R;
+                u64 g2[4];
+                uint2 mv = make_uint2(0x80808080u, 0x80808080u);
+                if (live) {
+                    wide_run8(reinterpret_cast<const TG*>(sg + r * ROW), g2);
+                    mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
+                    mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) g2[j] = 0ull;
+                }
+                const u64 ra2 = splat(s_r[k * W_BAND + r]);
+                u64 rs2 = 0ull;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const u64 u2 = mul2(mul2(g2[j], ra2), cf2[j]);
+                    const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scb2);
+                    const u64 mn = fma2(om2, u2, mo2);
+                    const u64 df2 = sub2(u2, mn);
+                    u64 res2 = fma2(df2, df2, eps2);
+                    if (!live) res2 = 0ull;
+                    colacc[j] = add2(colacc[j], res2);
+                    rs2 = add2(rs2, res2);
+                    float lo, hi;
+                    upk(mn, lo, hi);
+                    amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
+                    m2[i][j] = mn;
+                }
+                float lo, hi;
+                upk(rs2, lo, hi);
+                rsum[i] = lo + hi;
+            }
+            // tile absmax: the 8 lanes {c8 ^ 1} x {4 row groups} share a 16x16 tile
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+            const float A = fix_absmax(amax);
+            const bool fastq = recip_safe(A);
+            const float inv = 1.0f / A;
+            const u64 inv2 = splat(inv), nA2 = splat(-A);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = rsub + 4 * i;
+                if (brow + r < R) {
+                    uint32_t out[2];
+                    if (fastq) {
+                        u64 y[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const u64 q0 = mul2(m2[i][j], inv2);
+                            const u64 rem = fma2(q0, nA2, m2[i][j]);
+                            const u64 qq = fma2(rem, inv2, q0);          // correctly rounded m / A
+                            y[j] = add2(mul2(qq, c127), magic);          // rint(q * 127) in the low mantissa byte
+                        }
+                        out[0] = pack_codes4(y[0], y[1]);
+                        out[1] = pack_codes4(y[2], y[3]);
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            float v0, v1, v2, v3;
+                            upk(m2[i][2 * t], v0, v1);
+                            upk(m2[i][2 * t + 1], v2, v3);
+                            out[t] = ((uint32_t)quant_i8_div(v0, A) & 0xffu) | (((uint32_t)quant_i8_div(v1, A) & 0xffu) << 8) |
+                                     (((uint32_t)quant_i8_div(v2, A) & 0xffu) << 16) | (((uint32_t)quant_i8_div(v3, A) & 0xffu) << 24);
+                        }
+                    }
+                    *reinterpret_cast<uint2*>(reinterpret_cast<int8_t*>(d.m) + (int64_t)(brow + r) * C + col) = make_uint2(out[0], out[1]);
+                }
+            }
+            if (rsub == 0 && (c8 & 1) == 0) d.m_absmax[tile_id] = A;     // one lane per tile
+            // row sums over this warp's 64 columns: reduce over the 8 column groups
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = rsum[i];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (c8 == 0) s_row[warp * W_TR + k * W_BAND + rsub + 4 * i] = v;
+            }
+        }
+        if (!ok) break;
+        // column partials: the 4 row groups of a warp hold partial sums of the same 8 columns
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float lo, hi;
+                upk(colacc[j], lo, hi);
+                lo += __shfl_xor_sync(0xffffffffu, lo, 8);  hi += __shfl_xor_sync(0xffffffffu, hi, 8);
+                lo += __shfl_xor_sync(0xffffffffu, lo, 16); hi += __shfl_xor_sync(0xffffffffu, hi, 16);
+                if (rsub == 0) *reinterpret_cast<float2*>(s.colpart + (int64_t)it.tr * C + col + 2 * j) = make_float2(lo, hi);
+            }
+        }
+        __syncthreads();   // s_row complete; nobody reads s_r / s_c of this item any more
+        const int nw = (it.wcols + 63) >> 6;
+        for (int i = threadIdx.x; i < W_TR; i += W_THREADS) {
+            const int row = it.row0 + i;
+            if (row < R) {
+                float t = 0.0f;
+                for (int ww = 0; ww < nw; ++ww) t += s_row[ww * W_TR + i];
+                s.rowpart[(int64_t)it.tc * R + row] = t;
+            }
+        }
+        // the next item's factor staging starts with a barrier (inside block_vector_sum), which orders these
+        // reads of s_row before the next item's writes
+    }
+    if (!ok && threadIdx.x == 0) {
+        // a copy never landed: record it and give the copies in flight one more bounded chance to land in this
+        // CTA's shared memory before it is released
+        atomicExch(a.status, STATUS_MBAR_TIMEOUT);
+        for (int i = 0; i < STAGES; ++i) (void)mbar_wait(&bars[i], 0);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// apply pass (reference: kParamUpdateTiled came_kernels.cu:3332-3366, weight decay of :2678-2682)
+// ------------------------------------------------------------------------------------------------
+template <typename TP>
+__global__ void __launch_bounds__(W_THREADS, 1) k_apply_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+    constexpr int STAGES = WideCfg<TP>::STAGES, STAGE = WideCfg<TP>::STAGE, ROW = WideCfg<TP>::ROW;
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    float* s_r = reinterpret_cast<float*>(bars + 8);
+    float* s_c = s_r + W_TR;
+    float* red = s_c + W_TC;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c8 = lane & 7, rsub = lane >> 3;
+    const int cl = warp * 64 + c8 * 8;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) mbar_init(&bars[i], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    WideProducer<TP> prod;
+    if (warp == 0) {
+        prod.init(a, work, n_items, false);
+        for (int i = 0; i < STAGES - 1; ++i) prod.issue(a, work, n_items, false, smem, bars, lane);
+    }
+    int q = 0;
+    bool ok = true;
+
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const WideItem it = wide_item<TP>(a, work[item], false);
+        const CameTensorDesc& d = a.descs[it.tensor];
+        const Scratch& s = a.scr[it.tensor];
+        const CameHyper& h = a.hyp[d.group];
+        const int R = it.R, C = it.C;
+        const bool active = cl < it.wcols;
+        const int col = it.col0 + cl;
+        const int tile_cols = C >> 4;
+        {
+            const bool cr = d.flags & CAME_F_RESROW_CLAMP;
+            float mean = block_vector_sum(s.rowblk2, s.nbR, red) / (float)R;   // starts with a barrier: the previous
+            mean = guard_mean(mean, d.flags & CAME_F_RESROW_FIX, cr);          // item's readers of s_r / s_c are done
+            for (int i = threadIdx.x; i < W_TR; i += W_THREADS)
+                s_r[i] = (it.row0 + i < R) ? row_factor(s.Rr[it.row0 + i], mean, cr) : 0.0f;
+            for (int i = threadIdx.x; i < it.wcols; i += W_THREADS)
+                s_c[i] = col_factor(s.Rc[it.col0 + i], d.flags & CAME_F_RESCOL_CLAMP);
+            __syncthreads();
+        }
+        u64 cf2[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cf2[j] = active ? pk(s_c[cl + 2 * j], s_c[cl + 2 * j + 1]) : 0ull;
+        const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
+        float a_next = active ? amax_col[0] : 0.0f;     // tile absmax, fetched one band ahead
+        const bool decay = h.weight_decay != 0.0f;
+        const int wd_form = (d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 1 : 0);
+        const u64 dmul2 = splat(h.decay_mul), nwdlr2 = splat(-h.wd_lr), nlr2 = splat(-h.lr);
+
+#pragma unroll 1
+        for (int k = 0; k < it.nbands; ++k, ++q) {
+            const int slot = q % STAGES;
+            if (!__syncthreads_and(mbar_wait(&bars[slot], (q / STAGES) & 1))) { ok = false; break; }
+            if (warp == 0) prod.issue(a, work, n_items, false, smem, bars, lane);
+            if (!active) continue;
+            const unsigned char* sp = smem + slot * STAGE + cl * (int)sizeof(TP);
+            const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
+            const int brow = it.row0 + k * W_BAND;
+            const float A = a_next;
+            if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
+            const float sc = A > 0.0f ? A / QMAX_I8 : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = rsub + 4 * i;
+                if (brow + r < R) {
+                    u64 p2[4];
+                    wide_run8(reinterpret_cast<const TP*>(sp + r * ROW), p2);
+                    uint2 mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
+                    mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
+                    const u64 scr2 = splat(sc * s_r[k * W_BAND + r]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const u64 upd = mul2(mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scr2), cf2[j]);
+                        u64 pv = p2[j];
+                        if (decay) {
+                            if (wd_form == 2) pv = round_pair<TP>(mul2(pv, dmul2));
+                            else if (wd_form == 1) pv = round_pair<TP>(fma2(nwdlr2, pv, pv));
+                            else pv = fma2(nwdlr2, pv, pv);
+                        }
+                        p2[j] = fma2(nlr2, upd, pv);
+                    }
+                    wide_store8(reinterpret_cast<TP*>(d.p) + (int64_t)(brow + r) * C + col, p2);
+                }
+            }
+        }
+    }
+    if (!ok && threadIdx.x == 0) {
+        atomicExch(a.status, STATUS_MBAR_TIMEOUT);
+        for (int i = 0; i < STAGES; ++i) (void)mbar_wait(&bars[i], 0);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// launchers
+// ------------------------------------------------------------------------------------------------
+template <typename T> static constexpr size_t moment_smem() {
+    return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + 8 * sizeof(uint64_t) +
+           (W_TR + W_TC + W_WARPS * W_TR + 36) * sizeof(float);
+}
+template <typename T> static constexpr size_t apply_smem() {
+    return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + 8 * sizeof(uint64_t) + (W_TR + W_TC + 36) * sizeof(float);
+}
+
+template <typename K>
+static cudaError_t launch_persistent(K kernel, size_t smem, const StepArgs& a, const Work* work, int n, cudaStream_t st) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<n < sms ? n : sms, W_THREADS, smem, st>>>(a, work, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
+                              cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    if (kernel == KID_MOMENT) {
+        switch (key.g_dtype) {
+            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float>, moment_smem<float>(), a, work, n, st);
+            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half>, moment_smem<__half>(), a, work, n, st);
+            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16>, moment_smem<__nv_bfloat16>(), a, work, n, st);
+        }
+    }
+    if (kernel == KID_APPLY) {
+        switch (key.p_dtype) {
+            case CAME_DT_F32: return launch_persistent(k_apply_tile8_wide<float>, apply_smem<float>(), a, work, n, st);
+            case CAME_DT_F16: return launch_persistent(k_apply_tile8_wide<__half>, apply_smem<__half>(), a, work, n, st);
+            default: return launch_persistent(k_apply_tile8_wide<__nv_bfloat16>, apply_smem<__nv_bfloat16>(), a, work, n, st);
+        }
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace came

@@ -1,0 +1,267 @@
+// Fused first pass over the gradient: ONE read of g yields the row sums and column sums of g^2 (for the
+// factored second moment) AND the column sums of g^2 / v_row (from which S = sum (g r c)^2, the quantity the
+// RMS clip needs, follows without a second read of g):
+//
+//     S = sum_ij g_ij^2 r_i^2 c_j^2 = mean(v_row) * sum_j (1 / v_col_j) * T_j,   T_j = sum_i g_ij^2 / v_row_i
+//
+// which holds because r_i^2 = mean(v_row) / v_row_i and c_j^2 = 1 / v_col_j when no 1e-30 clamp is active
+// (tensors carrying CAME_F_SQ_CLAMP take the two-pass kernels instead).  v_row_i needs the complete row,
+// so a CTA owns whole rows: a strip of 128 rows, staged through shared memory in batches of `rb` rows by
+// bulk asynchronous copies (three slots: two batches in flight while one is computed on), swept twice from
+// shared memory.
+//
+// Replaces kUpdateSqRowQuantized, the column walk of kUpdateSqColQuantizedFinalize and kSumUpdateSq
+// (came_kernels.cu:61-96, 198-243, 596-619), which read g three times.
+#include "common.cuh"
+#include "launch.h"
+#include "pipeline.cuh"
+
+namespace came {
+
+constexpr int FA_THREADS = 512;
+constexpr int FA_WARPS = FA_THREADS / 32;
+constexpr int FA_STAGES = 3;
+constexpr int FA_RB_MAX = 16;
+
+// 8 consecutive staged elements -> 4 packed fp32 pairs
+__device__ __forceinline__ void smem_run8(const __nv_bfloat16* p, u64* out) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) out[j] = pk_u32(w[j] << 16, w[j] & 0xffff0000u);
+}
+__device__ __forceinline__ void smem_run8(const __half* p, u64* out) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        out[j] = pk(f.x, f.y);
+    }
+}
+__device__ __forceinline__ void smem_run8(const float* p, u64* out) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    out[0] = pk(a.x, a.y); out[1] = pk(a.z, a.w); out[2] = pk(b.x, b.y); out[3] = pk(b.z, b.w);
+}
+
+// Sum N per-lane values v[0..N) over the 32 lanes of a warp with a halving butterfly: after log2(N) exchange
+// steps every lane holds one row's partial, the remaining steps finish it.  Lane L ends with the total of row
+// (L >> (5 - log2 N)) & (N - 1)   (N = 16: (L >> 1) & 15, N = 8: (L >> 2) & 7, N = 4: (L >> 3) & 3).
+template <int N>
+__device__ __forceinline__ float warp_reduce_rows(float* v, int lane) {
+    int mask = 16;
+#pragma unroll
+    for (int n = N; n > 1; n >>= 1, mask >>= 1) {
+        const bool upper = (lane & mask) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = upper ? v[i] : v[i + n / 2];
+            const float keep = upper ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+        }
+    }
+    float t = v[0];
+#pragma unroll
+    for (; mask > 0; mask >>= 1) t += __shfl_xor_sync(0xffffffffu, t, mask);
+    return t;
+}
+
+template <typename TG, int NG>
+__global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const Work w = work[blockIdx.x];
+    const CameTensorDesc& d = a.descs[w.tensor];
+    const Scratch& s = a.scr[w.tensor];
+    const CameHyper& h = a.hyp[d.group];
+    const int R = (int)d.rows, C = (int)d.cols;
+    const int rb = s.fa_rb;
+    const int row_bytes = C * (int)sizeof(TG);
+    const int stage_bytes = rb * row_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_STAGES * stage_bytes);
+    float* s_part = reinterpret_cast<float*>(bars + FA_STAGES);      // [FA_WARPS][FA_RB_MAX]
+    float* s_w = s_part + FA_WARPS * FA_RB_MAX;                      // [FA_RB_MAX]
+
+    const int strip = w.tile;
+    const int row0 = strip * K_TR;
+    const int nrows = min(K_TR, R - row0);
+    const int nbatch = (nrows + rb - 1) / rb;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned char* g_src = reinterpret_cast<const unsigned char*>(d.g);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < FA_STAGES; ++i) mbar_init(&bars[i], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    auto issue = [&](int b) {   // warp 0: lane r copies row r of batch b
+        const int rows = min(rb, nrows - b * rb);
+        uint64_t* bar = &bars[b % FA_STAGES];
+        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)rows * (uint32_t)row_bytes);
+        __syncwarp();
+        if (lane < rows)
+            bulk_g2s(smem + (b % FA_STAGES) * stage_bytes + lane * row_bytes,
+                     g_src + (int64_t)(row0 + b * rb + lane) * row_bytes, (uint32_t)row_bytes, bar);
+    };
+    if (warp == 0) {
+        for (int b = 0; b < min(FA_STAGES, nbatch); ++b) issue(b);
+    }
+
+    // this thread's column groups: 8 consecutive columns starting at 8 * (threadIdx.x + FA_THREADS * j)
+    bool gvalid[NG];
+    u64 colb[NG][4], colT[NG][4];
+#pragma unroll
+    for (int j = 0; j < NG; ++j) {
+        gvalid[j] = (threadIdx.x + FA_THREADS * j) * 8 < C;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { colb[j][e] = 0ull; colT[j][e] = 0ull; }
+    }
+    const bool quant = d.mode != CAME_MODE_FP32;
+    bool ok = true;
+
+    for (int b = 0; b < nbatch; ++b) {
+        const int slot = b % FA_STAGES;
+        // uniform result of the bounded wait; also: every thread is done with batch b-1
+        if (!__syncthreads_and(mbar_wait(&bars[slot], (b / FA_STAGES) & 1))) { ok = false; break; }
+        if (warp == 0 && b >= 1 && b + FA_STAGES - 1 < nbatch) issue(b + FA_STAGES - 1);   // into the slot batch b-1 used
+        const int rows = min(rb, nrows - b * rb);
+        const unsigned char* st = smem + slot * stage_bytes;
+
+        // sweep 1: row sums and column sums of g^2.  Row partials of up to FA_RB_MAX rows stay in registers
+        // (static indices: the loops are fully unrolled and guarded) and are reduced across the warp together.
+        float rp[FA_RB_MAX];
+#pragma unroll
+        for (int r = 0; r < FA_RB_MAX; ++r) {
+            rp[r] = 0.0f;
+            if (r < rows) {
+                u64 racc = 0ull;
+#pragma unroll
+                for (int j = 0; j < NG; ++j) {
+                    if (gvalid[j]) {
+                        u64 g2[4];
+                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            colb[j][e] = fma2(g2[e], g2[e], colb[j][e]);
+                            racc = fma2(g2[e], g2[e], racc);
+                        }
+                    }
+                }
+                float lo, hi;
+                upk(racc, lo, hi);
+                rp[r] = lo + hi;
+            }
+        }
+        if (rows > 8) {
+            const float t = warp_reduce_rows<16>(rp, lane);
+            if ((lane & 1) == 0) s_part[warp * FA_RB_MAX + ((lane >> 1) & 15)] = t;
+        } else if (rows > 4) {
+            const float t = warp_reduce_rows<8>(rp, lane);
+            if ((lane & 3) == 0) s_part[warp * FA_RB_MAX + ((lane >> 2) & 7)] = t;
+        } else {
+            const float t = warp_reduce_rows<4>(rp, lane);
+            if ((lane & 7) == 0) s_part[warp * FA_RB_MAX + ((lane >> 3) & 3)] = t;
+        }
+        __syncthreads();
+        if (warp == 0 && lane < rows) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int ww = 0; ww < FA_WARPS; ++ww) sum += s_part[ww * FA_RB_MAX + lane];
+            const int row = row0 + b * rb + lane;
+            // mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the dequantised old state
+            const float mean = (sum + (float)C * h.eps0) / (float)C;
+            float old;
+            if (quant) old = (float)reinterpret_cast<const uint8_t*>(d.sq_row)[row] * (d.sq_row_absmax[row >> 8] / QMAX_U8);
+            else old = reinterpret_cast<const float*>(d.sq_row)[row];
+            const float v = old * h.beta2 + h.om_beta2 * mean;
+            s.vr[row] = v;
+            s_w[lane] = v > 0.0f ? 1.0f / v : 0.0f;
+        }
+        __syncthreads();
+        // sweep 2: column sums of g^2 / v_row
+#pragma unroll
+        for (int r = 0; r < FA_RB_MAX; ++r) {
+            if (r < rows) {
+                const u64 w2 = splat(s_w[r]);
+#pragma unroll
+                for (int j = 0; j < NG; ++j) {
+                    if (gvalid[j]) {
+                        u64 g2[4];
+                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) colT[j][e] = fma2(mul2(g2[e], g2[e]), w2, colT[j][e]);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) {
+        if (threadIdx.x == 0) {
+            atomicExch(a.status, STATUS_MBAR_TIMEOUT);
+            for (int i = 0; i < FA_STAGES; ++i) (void)mbar_wait(&bars[i], 0);
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < NG; ++j) {
+        if (gvalid[j]) {
+            const int64_t off = (int64_t)strip * C + (threadIdx.x + FA_THREADS * j) * 8;
+            float v[8], t[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                upk(colb[j][e], v[2 * e], v[2 * e + 1]);
+                upk(colT[j][e], t[2 * e], t[2 * e + 1]);
+            }
+            reinterpret_cast<float4*>(s.colpart + off)[0] = make_float4(v[0], v[1], v[2], v[3]);
+            reinterpret_cast<float4*>(s.colpart + off)[1] = make_float4(v[4], v[5], v[6], v[7]);
+            reinterpret_cast<float4*>(s.tpart + off)[0] = make_float4(t[0], t[1], t[2], t[3]);
+            reinterpret_cast<float4*>(s.tpart + off)[1] = make_float4(t[4], t[5], t[6], t[7]);
+        }
+    }
+}
+
+// rows per staged batch for a row of `row_bytes`: as many as fit 64 KB per slot, at most FA_RB_MAX
+int fused_sq_rows_per_batch(int64_t row_bytes) {
+    int64_t rb = (64 * 1024) / row_bytes;
+    if (rb > FA_RB_MAX) rb = FA_RB_MAX;
+    if (rb < 1) rb = 1;
+    return (int)rb;
+}
+
+bool fused_sq_eligible(int64_t cols, int elem_bytes) {
+    return cols % 8 == 0 && cols <= (int64_t)FA_THREADS * 8 * 4 && cols * elem_bytes <= 64 * 1024;
+}
+
+template <typename TG, int NG>
+static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, size_t smem, cudaStream_t st) {
+    cudaError_t e = cudaFuncSetAttribute(k_sqstat_fused<TG, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    k_sqstat_fused<TG, NG><<<n, FA_THREADS, smem, st>>>(a, work);
+    return cudaGetLastError();
+}
+
+template <typename TG>
+static cudaError_t launch_ng(int ng, const StepArgs& a, const Work* work, int n, size_t smem, cudaStream_t st) {
+    switch (ng) {
+        case 1: return launch_one<TG, 1>(a, work, n, smem, st);
+        case 2: return launch_one<TG, 2>(a, work, n, smem, st);
+        case 3: return launch_one<TG, 3>(a, work, n, smem, st);
+        default: return launch_one<TG, 4>(a, work, n, smem, st);
+    }
+}
+
+// key.mode carries the number of column groups per thread (1..4); all tensors of one launch share it and
+// `max_stage_bytes` is the largest slot (rows per batch x row bytes) among them
+cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_stage_bytes,
+                            cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    const size_t smem = FA_STAGES * max_stage_bytes + FA_STAGES * sizeof(uint64_t) +
+                        (FA_WARPS * FA_RB_MAX + FA_RB_MAX) * sizeof(float);
+    switch (key.g_dtype) {
+        case CAME_DT_F32: return launch_ng<float>(key.mode, a, work, n, smem, st);
+        case CAME_DT_F16: return launch_ng<__half>(key.mode, a, work, n, smem, st);
+        default: return launch_ng<__nv_bfloat16>(key.mode, a, work, n, smem, st);
+    }
+}
+
+}  // namespace came

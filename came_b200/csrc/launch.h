@@ -13,6 +13,7 @@ struct StepArgs {
     const CameTensorDesc* descs;   // device copy of the descriptor table
     const Scratch* scr;            // device, one per tensor
     const CameHyper* hyp;          // device, one per param_group
+    int* status;                   // device, one word: 0, or the STATUS_* code of a kernel that gave up a wait
 };
 
 // which template instance a work list is launched with
@@ -20,7 +21,7 @@ struct KernelKey {
     int g_dtype;
     int p_dtype;
     int mode;
-    bool vec;
+    int variant;   // 0: scalar loads, any shape; 1: 16-byte vector loads; 2: shared-memory staged fast path
 };
 
 enum KernelId {
@@ -40,6 +41,12 @@ enum KernelId {
 
 cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                             cudaStream_t st);
+cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
+                              cudaStream_t st);
+cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_stage_bytes,
+                            cudaStream_t st);
+int fused_sq_rows_per_batch(int64_t row_bytes);
+bool fused_sq_eligible(int64_t cols, int elem_bytes);
 cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                                cudaStream_t st);
 

@@ -142,6 +142,14 @@ class DevicePlan:
     def last_launches(self) -> int:
         return self.lib.came_b200_plan_last_launches(self.handle)
 
+    def status(self) -> int:
+        """Waits for the current stream and returns the plan's device status word (0 = fine)."""
+        out = C.c_int(0)
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            _lib.check(self.lib.came_b200_plan_status(self.handle, stream, C.byref(out)))
+        return out.value
+
     def set_timing(self, enable: bool) -> None:
         _lib.check(self.lib.came_b200_plan_set_timing(self.handle, int(enable)))
 

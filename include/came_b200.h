@@ -150,6 +150,14 @@ int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* c
  */
 int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, came_stream_t stream);
 
+/*
+ * Waits for `stream` and reads the plan's device status word: 0, or 1 when a kernel gave up waiting for a
+ * staged copy (every wait inside the kernels is bounded; the step's results are then incomplete).  The
+ * reference has no counterpart: it checks no launch or device error at all (no cudaGetLastError in
+ * came_kernels.cu).
+ */
+int came_b200_plan_status(came_plan_t* plan, came_stream_t stream, int* status);
+
 /* Number of kernel launches the last came_b200_step on this plan enqueued. */
 int came_b200_plan_last_launches(const came_plan_t* plan);
 
