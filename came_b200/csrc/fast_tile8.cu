@@ -1,7 +1,7 @@
 // Tile-layout (CAME8bit / CAME8bit2D) momentum and apply passes for matrices whose column count is a
 // multiple of 64 and whose buffers are 16-byte aligned.
 //
-// Persistent CTAs (one per SM, 512 threads) walk a strided share of the work list.  A work item is a tile of
+// Persistent CTAs (one per SM: 16 consumer warps + 1 producer warp) walk a strided share of the work list.  A work item is a tile of
 // 128 rows x up to 1024 columns, consumed in 8 bands of 16 rows.  Bands are staged in shared memory by bulk
 // asynchronous copies (TMA, one copy per row per operand: 2 KB / 1 KB, the size at which the copy engine
 // reaches full bandwidth) through a ring of mbarriers that runs ahead across item boundaries.  Arithmetic
@@ -15,6 +15,9 @@
 #include "common.cuh"
 #include "launch.h"
 #include "pipeline.cuh"
+
+#include <cstdio>
+#include <type_traits>
 
 namespace came {
 
@@ -126,32 +129,78 @@ __device__ __forceinline__ WideItem wide_item(const StepArgs& a, const Work& w, 
     return it;
 }
 
-// The producer (warp 0) walks the same item sequence as the consumers, a few bands ahead.
+// Warps 0..15 consume (compute); warp 16 produces: it only issues the copies, because a bulk-copy instruction
+// blocks while the copy engine's queue is full and a band's 32 copies keep it busy for about as long as the
+// consumers need for a band.  Per ring slot there is a "full" barrier (the producer's expect_tx + the copies'
+// bytes) and an "empty" barrier (one arrival per consumer warp).  Nobody synchronises CTA-wide inside the band
+// loop; consumer warps may drift apart by up to STAGES-1 bands.  A waiter that times out raises `abort` in
+// shared memory; everybody polls it.
+constexpr int W_CONSUMERS = W_THREADS;            // 512 consumer threads
+constexpr int W_ALL_THREADS = W_THREADS + 32;     // + the producer warp
+
+struct WideShared {
+    uint64_t full[4];
+    uint64_t empty[4];
+    uint64_t sync;     // barrier among the 16 warps between items (one arrival per warp)
+    int abort;
+    int pad;
+};
+
+// Bounded wait that also gives up when another warp raised `abort`.  On its own timeout it records the failure
+// in the plan's status word and raises `abort`, so that every other waiter of the CTA leaves too.
+__device__ __forceinline__ bool wide_wait(uint64_t* bar, uint32_t parity, WideShared* sh, const StepArgs& a, int lane) {
+    volatile int* abort = &sh->abort;
+    for (uint32_t i = 0; i < MBAR_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return *abort == 0;
+        if ((i & 15u) == 15u && *abort) return false;
+    }
+    if (lane == 0) { atomicExch(a.status, STATUS_MBAR_TIMEOUT); atomicExch(&sh->abort, 1); }
+    return false;
+}
+// all-warps barrier number `n` (0, 1, 2, ...) of this CTA, built on an mbarrier so that it is bounded too
+__device__ __forceinline__ bool wide_barrier(WideShared* sh, int n, const StepArgs& a, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sh->sync);
+    return wide_wait(&sh->sync, (uint32_t)n & 1u, sh, a, lane);
+}
+// after a failed wait: give the copies in flight one more bounded chance to land before the CTA's shared
+// memory is released
+__device__ __forceinline__ void wide_drain(WideShared* sh, int stages) {
+    for (int i = 0; i < stages; ++i)
+        for (uint32_t t = 0; t < (1u << 16); ++t)
+            if (mbar_try_wait(&sh->full[i], 0) || mbar_try_wait(&sh->full[i], 1)) break;
+}
+
+// The copy stream of one CTA: every band of every work item of the CTA, in consumption order.
 template <typename TA>
 struct WideProducer {
-    int item, band, q;     // next band to issue: work-list index, band inside it, position in the band stream
-    WideItem it;
+    static constexpr int STAGES = WideCfg<TA>::STAGES;
+    int item, band, q;
     bool live;
+    WideItem it;
     __device__ __forceinline__ void init(const StepArgs& a, const Work* work, int n_items, bool a_is_grad) {
         item = blockIdx.x; band = 0; q = 0;
         live = item < n_items;
         if (live) it = wide_item<TA>(a, work[item], a_is_grad);
     }
-    // all 32 lanes of warp 0 call this: lane L < 16 copies row L of A, lane L >= 16 row L-16 of the codes
-    __device__ __forceinline__ void issue(const StepArgs& a, const Work* work, int n_items, bool a_is_grad,
-                                          unsigned char* smem, uint64_t* bars, int lane) {
-        if (!live) return;
-        constexpr int STAGES = WideCfg<TA>::STAGES, STAGE = WideCfg<TA>::STAGE, ROW = WideCfg<TA>::ROW;
+    // issue the next band of the stream (all 32 lanes of warp 0 call this); false on a timed-out wait
+    __device__ __forceinline__ bool issue(const StepArgs& a, const Work* work, int n_items, bool a_is_grad,
+                                          unsigned char* smem, WideShared* sh, int lane) {
+        if (!live) return true;
+        constexpr int STAGE = WideCfg<TA>::STAGE, ROW = WideCfg<TA>::ROW;
         const int slot = q % STAGES;
+        if (q >= STAGES) {   // every consumer warp must have released the slot's previous band
+            if (!wide_wait(&sh->empty[slot], ((q / STAGES) - 1) & 1, sh, a, lane)) return false;
+        }
         const int rows = min(W_BAND, it.R - it.row0 - band * W_BAND);
         const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(TA), m_bytes = (uint32_t)it.wcols;
-        if (lane == 0) mbar_arrive_expect_tx(&bars[slot], (uint32_t)rows * (a_bytes + m_bytes));
+        if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (a_bytes + m_bytes));
         __syncwarp();
         const int r = lane & 15;
         if (r < rows) {
             const int64_t row = band * W_BAND + r;
-            if (lane < 16) bulk_g2s(smem + slot * STAGE + r * ROW, it.a_src + row * it.a_pitch, a_bytes, &bars[slot]);
-            else bulk_g2s(smem + slot * STAGE + W_BAND * ROW + r * W_MROW, it.m_src + row * it.m_pitch, m_bytes, &bars[slot]);
+            if (lane < 16) bulk_g2s(smem + slot * STAGE + r * ROW, it.a_src + row * it.a_pitch, a_bytes, &sh->full[slot]);
+            else bulk_g2s(smem + slot * STAGE + W_BAND * ROW + r * W_MROW, it.m_src + row * it.m_pitch, m_bytes, &sh->full[slot]);
         }
         ++q;
         if (++band == it.nbands) {
@@ -160,41 +209,67 @@ struct WideProducer {
             live = item < n_items;
             if (live) it = wide_item<TA>(a, work[item], a_is_grad);
         }
+        return true;
     }
 };
+
+// consumer side of one band: wait for the data
+__device__ __forceinline__ bool wide_wait_full(const StepArgs& a, WideShared* sh, int slot, int parity, int lane) {
+    return wide_wait(&sh->full[slot], (uint32_t)parity, sh, a, lane);
+}
+__device__ __forceinline__ void wide_release(WideShared* sh, int slot, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sh->empty[slot]);
+}
+
+// sum of x[0..n) computed by one warp (same order in every warp that calls it)
+__device__ __forceinline__ float warp_vector_sum(const float* x, int n, int lane) {
+    float t = 0.0f;
+    for (int i = lane; i < n; i += 32) t += x[i];
+    return warp_sum(t);
+}
 
 // ------------------------------------------------------------------------------------------------
 // momentum pass (reference: kUpdateExpAvgQuantAndResSumsTiled came_kernels.cu:2584-2683)
 // ------------------------------------------------------------------------------------------------
 template <typename TG>
-__global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+__global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
     constexpr int STAGES = WideCfg<TG>::STAGES, STAGE = WideCfg<TG>::STAGE, ROW = WideCfg<TG>::ROW;
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-    float* s_r = reinterpret_cast<float*>(bars + 8);
-    float* s_c = s_r + W_TR;
-    float* s_row = s_c + W_TC;                 // [W_WARPS][W_TR]
-    float* red = s_row + W_WARPS * W_TR;
+    WideShared* sh = reinterpret_cast<WideShared*>(smem + STAGES * STAGE);
+    float* s_r = reinterpret_cast<float*>(sh + 1);      // [2][W_TR]   row factors (times 1/clip), double-buffered by item
+    float* s_c = s_r + 2 * W_TR;                        // [2][W_TC]   column factors
+    float* s_row = s_c + 2 * W_TC;                      // [2][W_WARPS][W_TR]  per-warp row partials of the residual
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c8 = lane & 7, rsub = lane >> 3;
-    const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
-
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], W_WARPS); }
+        mbar_init(&sh->sync, W_WARPS);
+        sh->abort = 0;
         mbar_init_fence();
     }
     __syncthreads();
-    WideProducer<TG> prod;
-    if (warp == 0) {
+    if (warp == W_WARPS) {      // producer warp: run the copy stream as far ahead as the ring allows
+        WideProducer<TG> prod;
         prod.init(a, work, n_items, true);
-        for (int i = 0; i < STAGES - 1; ++i) prod.issue(a, work, n_items, true, smem, bars, lane);
+        while (prod.live && prod.issue(a, work, n_items, true, smem, sh, lane)) {}
+        return;
     }
+    const int c8 = lane & 7, rsub = lane >> 3;
+    const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
     const u64 c127 = splat(QMAX_I8), magic = splat(ROUND_MAGIC);
     int q = 0;            // position of the next band to consume in this CTA's band stream
-    bool ok = true;
+    int buf = 0, nsync = 0;
+    bool aborted = false;
+#ifdef CAME_WIDE_PROFILE
+    long long prof_issue = 0, prof_wait = 0, prof_bar = 0;
+    const long long prof_start = clock64();
+#endif
+    // epilogue of the previous item, finished after the next item's barrier (s_row is complete only then)
+    int prev_valid = 0, prev_row0 = 0, prev_R = 0, prev_tc = 0, prev_nw = 0, prev_nrows = 0;
+    float* prev_rowpart = nullptr;
 
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, buf ^= 1) {
         const WideItem it = wide_item<TG>(a, work[item], true);
         const CameTensorDesc& d = a.descs[it.tensor];
         const Scratch& s = a.scr[it.tensor];
@@ -203,21 +278,39 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
         const bool active = cl < it.wcols;        // warps beyond a ragged tile width idle
         const int col = it.col0 + cl;
         const int tile_cols = C >> 4;
+        float* sr = s_r + buf * W_TR;
+        float* sc = s_c + buf * W_TC;
+        float* srow = s_row + buf * (W_WARPS * W_TR);
         {   // row / column factors of this tile (same arithmetic as stage_factors in factored.cu)
             const bool clamp = d.flags & CAME_F_SQ_CLAMP;
-            float mean = block_vector_sum(s.rowblk, s.nbR, red) / (float)R;
+            float mean = warp_vector_sum(s.rowblk, s.nbR, lane) / (float)R;
             mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
             const float inv_clip = 1.0f / s.scal[1];
-            for (int i = threadIdx.x; i < W_TR; i += W_THREADS)
-                s_r[i] = (it.row0 + i < R) ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
-            for (int i = threadIdx.x; i < it.wcols; i += W_THREADS) s_c[i] = col_factor(s.vc[it.col0 + i], clamp);
-            __syncthreads();
+            for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS)
+                sr[i] = (it.row0 + i < R) ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
+            for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS) sc[i] = col_factor(s.vc[it.col0 + i], clamp);
+            // also: every warp has finished the previous item, whose row partials are complete now
+#ifdef CAME_WIDE_PROFILE
+            const long long tb = clock64();
+#endif
+            if (!wide_barrier(sh, nsync++, a, lane)) { aborted = true; break; }
+#ifdef CAME_WIDE_PROFILE
+            prof_bar += clock64() - tb;
+#endif
+        }
+        if (prev_valid) {   // row partials of the previous item: sum the per-warp shares in a fixed order
+            const float* prow = s_row + (buf ^ 1) * (W_WARPS * W_TR);
+            for (int i = threadIdx.x; i < prev_nrows; i += W_CONSUMERS) {
+                float t = 0.0f;
+                for (int ww = 0; ww < prev_nw; ++ww) t += prow[ww * W_TR + i];
+                prev_rowpart[(int64_t)prev_tc * prev_R + prev_row0 + i] = t;
+            }
         }
         u64 cf2[4], colacc[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            cf2[j] = active ? pk(s_c[cl + 2 * j], s_c[cl + 2 * j + 1]) : 0ull;
-            colacc[j] = 0ull;
+            cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
+            colacc[j] = F2ZERO;
         }
         // old tile absmax, fetched one band ahead: a dependent global load at the top of every band would sit
         // on the critical path of the iteration
@@ -225,15 +318,20 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
         float a_next = active ? amax_col[0] : 0.0f;
         const u64 om2 = splat(h.om_beta1), eps2 = splat(h.eps1);
         const float beta1 = h.beta1;
+        bool ok = true;
 
 #pragma unroll 1
         for (int k = 0; k < it.nbands; ++k, ++q) {
             const int slot = q % STAGES;
-            // The result of the bounded wait is made uniform over the CTA so that all warps leave together.
-            // The barrier also means every warp is done with the previous band, whose slot is refilled next.
-            if (!__syncthreads_and(mbar_wait(&bars[slot], (q / STAGES) & 1))) { ok = false; break; }
-            if (warp == 0) prod.issue(a, work, n_items, true, smem, bars, lane);
-            if (!active) continue;
+#ifdef CAME_WIDE_PROFILE
+            const long long t0 = clock64(), t1 = t0;
+#endif
+            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) { ok = false; break; }
+#ifdef CAME_WIDE_PROFILE
+            const long long t2 = clock64();
+            prof_issue += t1 - t0; prof_wait += t2 - t1;
+#endif
+            if (!active) { wide_release(sh, slot, lane); continue; }
             const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(TG);
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
             const int brow = it.row0 + k * W_BAND;
@@ -241,59 +339,53 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
             const float a_old = a_next;
             if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
             const u64 scb2 = splat(a_old > 0.0f ? (a_old / QMAX_I8) * beta1 : 0.0f);
-
-            u64 m2[4][4];
+            const bool full_band = brow + W_BAND <= R;     // uniform over the CTA
             float rsum[4];
-            float amax = 0.0f;
+            float A;
+            // FULL: all 16 rows of the band exist: no per-row predicate anywhere.  Otherwise (only the last band
+            // of a matrix whose row count is not a multiple of 16) rows past the end hold stale bytes in shared
+            // memory; whatever they produce is kept out of the sums, the absmax and the stores.
+            auto band = [&](auto full_tag) {
+                constexpr bool FULL = decltype(full_tag)::value;
+                u64 m2[4][4];
+                float amax = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = rsub + 4 * i;
-                const bool live = brow + r < R;
-                u64 g2[4];
-                uint2 mv = make_uint2(0x80808080u, 0x80808080u);
-                if (live) {
+                for (int i = 0; i < 4; ++i) {
+                    const int r = rsub + 4 * i;
+                    const bool live = FULL || (brow + r < R);
+                    u64 g2[4];
                     wide_run8(reinterpret_cast<const TG*>(sg + r * ROW), g2);
-                    mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
+                    uint2 mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
                     mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
-                } else {
+                    const u64 ra2 = splat(live ? sr[k * W_BAND + r] : 0.0f);
+                    u64 rs2 = F2ZERO;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) g2[j] = 0ull;
+                    for (int j = 0; j < 4; ++j) {
+                        const u64 u2 = mul2(mul2(g2[j], ra2), cf2[j]);
+                        const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scb2);
+                        u64 mn = fma2(om2, u2, mo2);
+                        const u64 df2 = sub2(u2, mn);
+                        u64 res2 = fma2(df2, df2, eps2);
+                        if (!FULL && !live) { res2 = F2ZERO; mn = F2ZERO; }
+                        colacc[j] = add2(colacc[j], res2);
+                        rs2 = add2(rs2, res2);
+                        amax = fmaxf(amax, fmaxf(fabsf(mn.x), fabsf(mn.y)));
+                        m2[i][j] = mn;
+                    }
+                    rsum[i] = rs2.x + rs2.y;
                 }
-                const u64 ra2 = splat(s_r[k * W_BAND + r]);
-                u64 rs2 = 0ull;
+                wide_release(sh, slot, lane);      // the slot's bytes are in registers now
+                // tile absmax: the 8 lanes {c8 ^ 1} x {4 row groups} share a 16x16 tile
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+                A = fix_absmax(amax);
+                int8_t* mdst = reinterpret_cast<int8_t*>(d.m) + (int64_t)(brow + rsub) * C + col;
+                // the reciprocal form needs a normal 1/A: decided per warp so that the branch never diverges
+                if (__all_sync(0xffffffffu, recip_safe(A))) {
+                    const u64 inv2 = splat(1.0f / A), nA2 = splat(-A);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const u64 u2 = mul2(mul2(g2[j], ra2), cf2[j]);
-                    const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scb2);
-                    const u64 mn = fma2(om2, u2, mo2);
-                    const u64 df2 = sub2(u2, mn);
-                    u64 res2 = fma2(df2, df2, eps2);
-                    if (!live) res2 = 0ull;
-                    colacc[j] = add2(colacc[j], res2);
-                    rs2 = add2(rs2, res2);
-                    float lo, hi;
-                    upk(mn, lo, hi);
-                    amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
-                    m2[i][j] = mn;
-                }
-                float lo, hi;
-                upk(rs2, lo, hi);
-                rsum[i] = lo + hi;
-            }
-            // tile absmax: the 8 lanes {c8 ^ 1} x {4 row groups} share a 16x16 tile
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
-            const float A = fix_absmax(amax);
-            const bool fastq = recip_safe(A);
-            const float inv = 1.0f / A;
-            const u64 inv2 = splat(inv), nA2 = splat(-A);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = rsub + 4 * i;
-                if (brow + r < R) {
-                    uint32_t out[2];
-                    if (fastq) {
+                    for (int i = 0; i < 4; ++i) {
                         u64 y[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -302,21 +394,26 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
                             const u64 qq = fma2(rem, inv2, q0);          // correctly rounded m / A
                             y[j] = add2(mul2(qq, c127), magic);          // rint(q * 127) in the low mantissa byte
                         }
-                        out[0] = pack_codes4(y[0], y[1]);
-                        out[1] = pack_codes4(y[2], y[3]);
-                    } else {
+                        if (FULL || brow + rsub + 4 * i < R)
+                            *reinterpret_cast<uint2*>(mdst + (int64_t)(4 * i) * C) = make_uint2(pack_codes4(y[0], y[1]), pack_codes4(y[2], y[3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t out[2];
 #pragma unroll
                         for (int t = 0; t < 2; ++t) {
-                            float v0, v1, v2, v3;
-                            upk(m2[i][2 * t], v0, v1);
-                            upk(m2[i][2 * t + 1], v2, v3);
-                            out[t] = ((uint32_t)quant_i8_div(v0, A) & 0xffu) | (((uint32_t)quant_i8_div(v1, A) & 0xffu) << 8) |
-                                     (((uint32_t)quant_i8_div(v2, A) & 0xffu) << 16) | (((uint32_t)quant_i8_div(v3, A) & 0xffu) << 24);
+                            const u64 lo2 = m2[i][2 * t], hi2 = m2[i][2 * t + 1];
+                            out[t] = ((uint32_t)quant_i8_div(lo2.x, A) & 0xffu) | (((uint32_t)quant_i8_div(lo2.y, A) & 0xffu) << 8) |
+                                     (((uint32_t)quant_i8_div(hi2.x, A) & 0xffu) << 16) | (((uint32_t)quant_i8_div(hi2.y, A) & 0xffu) << 24);
                         }
+                        if (FULL || brow + rsub + 4 * i < R)
+                            *reinterpret_cast<uint2*>(mdst + (int64_t)(4 * i) * C) = make_uint2(out[0], out[1]);
                     }
-                    *reinterpret_cast<uint2*>(reinterpret_cast<int8_t*>(d.m) + (int64_t)(brow + r) * C + col) = make_uint2(out[0], out[1]);
                 }
-            }
+            };
+            if (full_band) band(std::true_type{});
+            else band(std::false_type{});
             if (rsub == 0 && (c8 & 1) == 0) d.m_absmax[tile_id] = A;     // one lane per tile
             // row sums over this warp's 64 columns: reduce over the 8 column groups
 #pragma unroll
@@ -325,10 +422,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 4);
-                if (c8 == 0) s_row[warp * W_TR + k * W_BAND + rsub + 4 * i] = v;
+                if (c8 == 0) srow[warp * W_TR + k * W_BAND + rsub + 4 * i] = v;
             }
         }
-        if (!ok) break;
+        if (!ok) { aborted = true; break; }
         // column partials: the 4 row groups of a warp hold partial sums of the same 8 columns
         if (active) {
 #pragma unroll
@@ -340,24 +437,26 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
                 if (rsub == 0) *reinterpret_cast<float2*>(s.colpart + (int64_t)it.tr * C + col + 2 * j) = make_float2(lo, hi);
             }
         }
-        __syncthreads();   // s_row complete; nobody reads s_r / s_c of this item any more
-        const int nw = (it.wcols + 63) >> 6;
-        for (int i = threadIdx.x; i < W_TR; i += W_THREADS) {
-            const int row = it.row0 + i;
-            if (row < R) {
-                float t = 0.0f;
-                for (int ww = 0; ww < nw; ++ww) t += s_row[ww * W_TR + i];
-                s.rowpart[(int64_t)it.tc * R + row] = t;
-            }
-        }
-        // the next item's factor staging starts with a barrier (inside block_vector_sum), which orders these
-        // reads of s_row before the next item's writes
+        prev_valid = 1; prev_row0 = it.row0; prev_R = R; prev_tc = it.tc; prev_nw = (it.wcols + 63) >> 6;
+        prev_nrows = min(W_TR, R - it.row0); prev_rowpart = s.rowpart;
     }
-    if (!ok && threadIdx.x == 0) {
-        // a copy never landed: record it and give the copies in flight one more bounded chance to land in this
-        // CTA's shared memory before it is released
-        atomicExch(a.status, STATUS_MBAR_TIMEOUT);
-        for (int i = 0; i < STAGES; ++i) (void)mbar_wait(&bars[i], 0);
+#ifdef CAME_WIDE_PROFILE
+    if ((blockIdx.x == 0 || blockIdx.x == 77) && lane == 0 && (warp == 0 || warp == 5 || warp == 15))
+        printf("moment cta %d warp %d: total %lld issue %lld wait_full %lld item_barrier %lld bands %d\n", blockIdx.x, warp,
+               clock64() - prof_start, prof_issue, prof_wait, prof_bar, q);
+#endif
+    // after this barrier the last item's row partials are complete; a warp that gave up a wait skips it
+    if (aborted || !wide_barrier(sh, nsync++, a, lane)) {
+        if (warp == 0) wide_drain(sh, STAGES);
+        return;
+    }
+    if (prev_valid) {
+        const float* prow = s_row + (buf ^ 1) * (W_WARPS * W_TR);
+        for (int i = threadIdx.x; i < prev_nrows; i += W_CONSUMERS) {
+            float t = 0.0f;
+            for (int ww = 0; ww < prev_nw; ++ww) t += prow[ww * W_TR + i];
+            prev_rowpart[(int64_t)prev_tc * prev_R + prev_row0 + i] = t;
+        }
     }
 }
 
@@ -365,32 +464,33 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_moment_tile8_wide(StepArgs a, 
 // apply pass (reference: kParamUpdateTiled came_kernels.cu:3332-3366, weight decay of :2678-2682)
 // ------------------------------------------------------------------------------------------------
 template <typename TP>
-__global__ void __launch_bounds__(W_THREADS, 1) k_apply_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+__global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
     constexpr int STAGES = WideCfg<TP>::STAGES, STAGE = WideCfg<TP>::STAGE, ROW = WideCfg<TP>::ROW;
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-    float* s_r = reinterpret_cast<float*>(bars + 8);
-    float* s_c = s_r + W_TR;
-    float* red = s_c + W_TC;
+    WideShared* sh = reinterpret_cast<WideShared*>(smem + STAGES * STAGE);
+    float* s_r = reinterpret_cast<float*>(sh + 1);      // [2][W_TR]
+    float* s_c = s_r + 2 * W_TR;                        // [2][W_TC]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c8 = lane & 7, rsub = lane >> 3;
-    const int cl = warp * 64 + c8 * 8;
-
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], W_WARPS); }
+        mbar_init(&sh->sync, W_WARPS);
+        sh->abort = 0;
         mbar_init_fence();
     }
     __syncthreads();
-    WideProducer<TP> prod;
-    if (warp == 0) {
+    if (warp == W_WARPS) {      // producer warp: run the copy stream as far ahead as the ring allows
+        WideProducer<TP> prod;
         prod.init(a, work, n_items, false);
-        for (int i = 0; i < STAGES - 1; ++i) prod.issue(a, work, n_items, false, smem, bars, lane);
+        while (prod.live && prod.issue(a, work, n_items, false, smem, sh, lane)) {}
+        return;
     }
-    int q = 0;
-    bool ok = true;
+    const int c8 = lane & 7, rsub = lane >> 3;
+    const int cl = warp * 64 + c8 * 8;
+    int q = 0, buf = 0, nsync = 0;
+    bool aborted = false;
 
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, buf ^= 1) {
         const WideItem it = wide_item<TP>(a, work[item], false);
         const CameTensorDesc& d = a.descs[it.tensor];
         const Scratch& s = a.scr[it.tensor];
@@ -399,77 +499,85 @@ __global__ void __launch_bounds__(W_THREADS, 1) k_apply_tile8_wide(StepArgs a, c
         const bool active = cl < it.wcols;
         const int col = it.col0 + cl;
         const int tile_cols = C >> 4;
+        float* sr = s_r + buf * W_TR;
+        float* sc = s_c + buf * W_TC;
         {
             const bool cr = d.flags & CAME_F_RESROW_CLAMP;
-            float mean = block_vector_sum(s.rowblk2, s.nbR, red) / (float)R;   // starts with a barrier: the previous
-            mean = guard_mean(mean, d.flags & CAME_F_RESROW_FIX, cr);          // item's readers of s_r / s_c are done
-            for (int i = threadIdx.x; i < W_TR; i += W_THREADS)
-                s_r[i] = (it.row0 + i < R) ? row_factor(s.Rr[it.row0 + i], mean, cr) : 0.0f;
-            for (int i = threadIdx.x; i < it.wcols; i += W_THREADS)
-                s_c[i] = col_factor(s.Rc[it.col0 + i], d.flags & CAME_F_RESCOL_CLAMP);
-            __syncthreads();
+            float mean = warp_vector_sum(s.rowblk2, s.nbR, lane) / (float)R;
+            mean = guard_mean(mean, d.flags & CAME_F_RESROW_FIX, cr);
+            for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS)
+                sr[i] = (it.row0 + i < R) ? row_factor(s.Rr[it.row0 + i], mean, cr) : 0.0f;
+            for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS)
+                sc[i] = col_factor(s.Rc[it.col0 + i], d.flags & CAME_F_RESCOL_CLAMP);
+            if (!wide_barrier(sh, nsync++, a, lane)) { aborted = true; break; }
         }
         u64 cf2[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cf2[j] = active ? pk(s_c[cl + 2 * j], s_c[cl + 2 * j + 1]) : 0ull;
+        for (int j = 0; j < 4; ++j) cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
         const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
         float a_next = active ? amax_col[0] : 0.0f;     // tile absmax, fetched one band ahead
         const bool decay = h.weight_decay != 0.0f;
         const int wd_form = (d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 1 : 0);
         const u64 dmul2 = splat(h.decay_mul), nwdlr2 = splat(-h.wd_lr), nlr2 = splat(-h.lr);
+        bool ok = true;
 
 #pragma unroll 1
         for (int k = 0; k < it.nbands; ++k, ++q) {
             const int slot = q % STAGES;
-            if (!__syncthreads_and(mbar_wait(&bars[slot], (q / STAGES) & 1))) { ok = false; break; }
-            if (warp == 0) prod.issue(a, work, n_items, false, smem, bars, lane);
-            if (!active) continue;
+            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) { ok = false; break; }
+            if (!active) { wide_release(sh, slot, lane); continue; }
             const unsigned char* sp = smem + slot * STAGE + cl * (int)sizeof(TP);
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
             const int brow = it.row0 + k * W_BAND;
+            const bool full_band = brow + W_BAND <= R;
             const float A = a_next;
             if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
-            const float sc = A > 0.0f ? A / QMAX_I8 : 0.0f;
+            const float scl = A > 0.0f ? A / QMAX_I8 : 0.0f;
+            u64 p2[4][4];
+            uint2 mv[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int r = rsub + 4 * i;
-                if (brow + r < R) {
-                    u64 p2[4];
-                    wide_run8(reinterpret_cast<const TP*>(sp + r * ROW), p2);
-                    uint2 mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
-                    mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
-                    const u64 scr2 = splat(sc * s_r[k * W_BAND + r]);
+                wide_run8(reinterpret_cast<const TP*>(sp + r * ROW), p2[i]);
+                mv[i] = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
+            }
+            float rfac[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const u64 upd = mul2(mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scr2), cf2[j]);
-                        u64 pv = p2[j];
-                        if (decay) {
-                            if (wd_form == 2) pv = round_pair<TP>(mul2(pv, dmul2));
-                            else if (wd_form == 1) pv = round_pair<TP>(fma2(nwdlr2, pv, pv));
-                            else pv = fma2(nwdlr2, pv, pv);
-                        }
-                        p2[j] = fma2(nlr2, upd, pv);
+            for (int i = 0; i < 4; ++i) rfac[i] = sr[k * W_BAND + rsub + 4 * i];
+            wide_release(sh, slot, lane);
+            TP* pdst = reinterpret_cast<TP*>(d.p) + (int64_t)(brow + rsub) * C + col;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t mx = mv[i].x ^ 0x80808080u, my = mv[i].y ^ 0x80808080u;
+                const u64 scr2 = splat(scl * rfac[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const u64 upd = mul2(mul2(codes_to_f2(j < 2 ? mx : my, (j & 1) * 2), scr2), cf2[j]);
+                    u64 pv = p2[i][j];
+                    if (decay) {
+                        if (wd_form == 2) pv = round_pair<TP>(mul2(pv, dmul2));
+                        else if (wd_form == 1) pv = round_pair<TP>(fma2(nwdlr2, pv, pv));
+                        else pv = fma2(nwdlr2, pv, pv);
                     }
-                    wide_store8(reinterpret_cast<TP*>(d.p) + (int64_t)(brow + r) * C + col, p2);
+                    p2[i][j] = fma2(nlr2, upd, pv);
                 }
+                if (full_band || brow + rsub + 4 * i < R) wide_store8(pdst + (int64_t)(4 * i) * C, p2[i]);
             }
         }
+        if (!ok) { aborted = true; break; }
     }
-    if (!ok && threadIdx.x == 0) {
-        atomicExch(a.status, STATUS_MBAR_TIMEOUT);
-        for (int i = 0; i < STAGES; ++i) (void)mbar_wait(&bars[i], 0);
-    }
+    if (aborted && warp == 0) wide_drain(sh, STAGES);
 }
 
 // ------------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------------
 template <typename T> static constexpr size_t moment_smem() {
-    return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + 8 * sizeof(uint64_t) +
-           (W_TR + W_TC + W_WARPS * W_TR + 36) * sizeof(float);
+    return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + sizeof(WideShared) +
+           2 * (W_TR + W_TC + W_WARPS * W_TR) * sizeof(float);
 }
 template <typename T> static constexpr size_t apply_smem() {
-    return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + 8 * sizeof(uint64_t) + (W_TR + W_TC + 36) * sizeof(float);
+    return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + sizeof(WideShared) + 2 * (W_TR + W_TC) * sizeof(float);
 }
 
 template <typename K>
@@ -483,7 +591,7 @@ static cudaError_t launch_persistent(K kernel, size_t smem, const StepArgs& a, c
     }
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    kernel<<<n < sms ? n : sms, W_THREADS, smem, st>>>(a, work, n);
+    kernel<<<n < sms ? n : sms, W_ALL_THREADS, smem, st>>>(a, work, n);
     return cudaGetLastError();
 }
 

@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
     for (int j = 0; j < NG; ++j) {
         gvalid[j] = (threadIdx.x + FA_THREADS * j) * 8 < C;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { colb[j][e] = 0ull; colT[j][e] = 0ull; }
+        for (int e = 0; e < 4; ++e) { colb[j][e] = F2ZERO; colT[j][e] = F2ZERO; }
     }
     const bool quant = d.mode != CAME_MODE_FP32;
     bool ok = true;
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
         for (int r = 0; r < FA_RB_MAX; ++r) {
             rp[r] = 0.0f;
             if (r < rows) {
-                u64 racc = 0ull;
+                u64 racc = F2ZERO;
 #pragma unroll
                 for (int j = 0; j < NG; ++j) {
                     if (gvalid[j]) {

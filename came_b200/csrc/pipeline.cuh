@@ -8,8 +8,6 @@
 
 namespace came {
 
-typedef unsigned long long u64;
-
 constexpr uint32_t MBAR_SPIN_LIMIT = 1u << 22;   // try_wait suspends for a hardware time slice per call
 constexpr int STATUS_MBAR_TIMEOUT = 1;
 
@@ -37,6 +35,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// barrier among the first `nthreads` threads of the CTA (a multiple of 32), leaving the other warps out
+__device__ __forceinline__ void named_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 // bounded wait; false on timeout
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (uint32_t i = 0; i < MBAR_SPIN_LIMIT; ++i)
@@ -50,40 +55,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  : "memory");
 }
 
-// ---- packed fp32x2 (two independent IEEE fp32 operations per instruction) -------------------------
-__device__ __forceinline__ u64 pk(float lo, float hi) {
-    u64 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ u64 pk_u32(uint32_t lo, uint32_t hi) {
-    u64 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-    return r;
-}
-__device__ __forceinline__ void upk(u64 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ void upk_u32(u64 v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
-__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
-    u64 d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
-    u64 d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ u64 add2(u64 a, u64 b) {
-    u64 d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
-    u64 d;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ u64 splat(float x) { return pk(x, x); }
+// ---- packed fp32x2 (two independent IEEE fp32 operations per instruction, sm_100 FFMA2 / FADD2 / FMUL2) ----
+typedef float2 u64;   // a pair of fp32 values living in an aligned register pair
+#define F2ZERO make_float2(0.0f, 0.0f)
+__device__ __forceinline__ u64 pk(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ u64 pk_u32(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
+__device__ __forceinline__ void upk(u64 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
+__device__ __forceinline__ void upk_u32(u64 v, uint32_t& lo, uint32_t& hi) { lo = __float_as_uint(v.x); hi = __float_as_uint(v.y); }
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ u64 add2(u64 a, u64 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) { return __fadd2_rn(a, make_float2(-b.x, -b.y)); }
+__device__ __forceinline__ u64 splat(float x) { return make_float2(x, x); }
 
 // two int8 codes (bytes `b`, `b+1` of the word `x`, already biased by ^0x80) -> packed exact floats:
 // the byte is dropped into the mantissa of 2^23, then 2^23 + 128 is subtracted
