@@ -141,7 +141,6 @@ constexpr int W_ALL_THREADS = W_THREADS + 32;     // + the producer warp
 struct WideShared {
     uint64_t full[4];
     uint64_t empty[4];
-    uint64_t sync;     // barrier among the 16 warps between items (one arrival per warp)
     int abort;
     int pad;
 };
@@ -156,12 +155,6 @@ __device__ __forceinline__ bool wide_wait(uint64_t* bar, uint32_t parity, WideSh
     }
     if (lane == 0) { atomicExch(a.status, STATUS_MBAR_TIMEOUT); atomicExch(&sh->abort, 1); }
     return false;
-}
-// all-warps barrier number `n` (0, 1, 2, ...) of this CTA, built on an mbarrier so that it is bounded too
-__device__ __forceinline__ bool wide_barrier(WideShared* sh, int n, const StepArgs& a, int lane) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&sh->sync);
-    return wide_wait(&sh->sync, (uint32_t)n & 1u, sh, a, lane);
 }
 // after a failed wait: give the copies in flight one more bounded chance to land before the CTA's shared
 // memory is released
@@ -244,7 +237,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], W_WARPS); }
-        mbar_init(&sh->sync, W_WARPS);
         sh->abort = 0;
         mbar_init_fence();
     }
@@ -259,7 +251,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
     const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
     const u64 c127 = splat(QMAX_I8), magic = splat(ROUND_MAGIC);
     int q = 0;            // position of the next band to consume in this CTA's band stream
-    int buf = 0, nsync = 0;
+    int buf = 0;
     bool aborted = false;
 #ifdef CAME_WIDE_PROFILE
     long long prof_issue = 0, prof_wait = 0, prof_bar = 0;
@@ -281,7 +273,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         float* sr = s_r + buf * W_TR;
         float* sc = s_c + buf * W_TC;
         float* srow = s_row + buf * (W_WARPS * W_TR);
-        {   // row / column factors of this tile (same arithmetic as stage_factors in factored.cu)
+        if (!aborted) {   // row / column factors of this tile (same arithmetic as stage_factors in factored.cu)
             const bool clamp = d.flags & CAME_F_SQ_CLAMP;
             float mean = warp_vector_sum(s.rowblk, s.nbR, lane) / (float)R;
             mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
@@ -289,14 +281,18 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS)
                 sr[i] = (it.row0 + i < R) ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
             for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS) sc[i] = col_factor(s.vc[it.col0 + i], clamp);
-            // also: every warp has finished the previous item, whose row partials are complete now
+        }
+        {
+            // also: every warp has finished the previous item, whose row partials are complete now.  A warp that
+            // gave up a wait still comes here once per item (see below), so this hardware barrier cannot hang.
 #ifdef CAME_WIDE_PROFILE
             const long long tb = clock64();
 #endif
-            if (!wide_barrier(sh, nsync++, a, lane)) { aborted = true; break; }
+            named_sync(1, W_CONSUMERS);
 #ifdef CAME_WIDE_PROFILE
             prof_bar += clock64() - tb;
 #endif
+            if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) { aborted = true; continue; }
         }
         if (prev_valid) {   // row partials of the previous item: sum the per-warp shares in a fixed order
             const float* prow = s_row + (buf ^ 1) * (W_WARPS * W_TR);
@@ -383,17 +379,17 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 int8_t* mdst = reinterpret_cast<int8_t*>(d.m) + (int64_t)(brow + rsub) * C + col;
                 // the reciprocal form needs a normal 1/A: decided per warp so that the branch never diverges
                 if (__all_sync(0xffffffffu, recip_safe(A))) {
-                    const u64 inv2 = splat(1.0f / A), nA2 = splat(-A);
+                    // code = rint((m / A) * 127) computed as rint((m * (1/A)) * 127): the quotient may differ from
+                    // the IEEE one in its last bit, which moves a code only when (m/A)*127 lies within ~1e-5 of a
+                    // rounding boundary (the reference kernel multiplies by a reciprocal as well,
+                    // came_kernels.cu:833-836).  The product and the rounding constant go through one FMA; the
+                    // sum's low mantissa byte is the two's-complement code.
+                    const u64 inv2 = splat(1.0f / A);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         u64 y[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const u64 q0 = mul2(m2[i][j], inv2);
-                            const u64 rem = fma2(q0, nA2, m2[i][j]);
-                            const u64 qq = fma2(rem, inv2, q0);          // correctly rounded m / A
-                            y[j] = add2(mul2(qq, c127), magic);          // rint(q * 127) in the low mantissa byte
-                        }
+                        for (int j = 0; j < 4; ++j) y[j] = fma2(mul2(m2[i][j], inv2), c127, magic);
                         if (FULL || brow + rsub + 4 * i < R)
                             *reinterpret_cast<uint2*>(mdst + (int64_t)(4 * i) * C) = make_uint2(pack_codes4(y[0], y[1]), pack_codes4(y[2], y[3]));
                     }
@@ -415,17 +411,19 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             if (full_band) band(std::true_type{});
             else band(std::false_type{});
             if (rsub == 0 && (c8 & 1) == 0) d.m_absmax[tile_id] = A;     // one lane per tile
-            // row sums over this warp's 64 columns: reduce over the 8 column groups
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float v = rsum[i];
+            // row sums over this warp's 64 columns: halving butterfly over the 8 column groups (4 shuffles instead
+            // of 12); lane c8 ends up with the sum of row rsub + 4 * ((c8 >> 1) & 3) when c8 is even
+            {
+                const bool up4 = (c8 & 4) != 0, up2 = (c8 & 2) != 0;
+                const float a0 = (up4 ? rsum[2] : rsum[0]) + __shfl_xor_sync(0xffffffffu, up4 ? rsum[0] : rsum[2], 4);
+                const float a1 = (up4 ? rsum[3] : rsum[1]) + __shfl_xor_sync(0xffffffffu, up4 ? rsum[1] : rsum[3], 4);
+                float v = (up2 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, up2 ? a0 : a1, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                v += __shfl_xor_sync(0xffffffffu, v, 4);
-                if (c8 == 0) srow[warp * W_TR + k * W_BAND + rsub + 4 * i] = v;
+                const int irow = (up4 ? 2 : 0) + (up2 ? 1 : 0);
+                if ((c8 & 1) == 0) srow[warp * W_TR + k * W_BAND + rsub + 4 * irow] = v;
             }
         }
-        if (!ok) { aborted = true; break; }
+        if (!ok) { aborted = true; continue; }
         // column partials: the 4 row groups of a warp hold partial sums of the same 8 columns
         if (active) {
 #pragma unroll
@@ -445,8 +443,9 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         printf("moment cta %d warp %d: total %lld issue %lld wait_full %lld item_barrier %lld bands %d\n", blockIdx.x, warp,
                clock64() - prof_start, prof_issue, prof_wait, prof_bar, q);
 #endif
-    // after this barrier the last item's row partials are complete; a warp that gave up a wait skips it
-    if (aborted || !wide_barrier(sh, nsync++, a, lane)) {
+    // after this barrier the last item's row partials are complete
+    named_sync(1, W_CONSUMERS);
+    if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) {
         if (warp == 0) wide_drain(sh, STAGES);
         return;
     }
@@ -474,7 +473,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], W_WARPS); }
-        mbar_init(&sh->sync, W_WARPS);
         sh->abort = 0;
         mbar_init_fence();
     }
@@ -487,7 +485,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
     }
     const int c8 = lane & 7, rsub = lane >> 3;
     const int cl = warp * 64 + c8 * 8;
-    int q = 0, buf = 0, nsync = 0;
+    int q = 0, buf = 0;
     bool aborted = false;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, buf ^= 1) {
@@ -501,7 +499,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
         const int tile_cols = C >> 4;
         float* sr = s_r + buf * W_TR;
         float* sc = s_c + buf * W_TC;
-        {
+        if (!aborted) {
             const bool cr = d.flags & CAME_F_RESROW_CLAMP;
             float mean = warp_vector_sum(s.rowblk2, s.nbR, lane) / (float)R;
             mean = guard_mean(mean, d.flags & CAME_F_RESROW_FIX, cr);
@@ -509,8 +507,10 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
                 sr[i] = (it.row0 + i < R) ? row_factor(s.Rr[it.row0 + i], mean, cr) : 0.0f;
             for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS)
                 sc[i] = col_factor(s.Rc[it.col0 + i], d.flags & CAME_F_RESCOL_CLAMP);
-            if (!wide_barrier(sh, nsync++, a, lane)) { aborted = true; break; }
         }
+        // hardware barrier among the consumer warps, met once per item even after a failed wait
+        named_sync(1, W_CONSUMERS);
+        if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) { aborted = true; continue; }
         u64 cf2[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
@@ -564,7 +564,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
                 if (full_band || brow + rsub + 4 * i < R) wide_store8(pdst + (int64_t)(4 * i) * C, p2[i]);
             }
         }
-        if (!ok) { aborted = true; break; }
+        if (!ok) { aborted = true; continue; }
     }
     if (aborted && warp == 0) wide_drain(sh, STAGES);
 }

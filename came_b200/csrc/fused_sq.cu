@@ -66,8 +66,29 @@ __device__ __forceinline__ float warp_reduce_rows(float* v, int lane) {
     return t;
 }
 
+// Shared bookkeeping of one CTA: ring barriers and the abort flag every waiter polls (same protocol as the momentum / apply passes).
+struct FaShared {
+    uint64_t full[FA_STAGES];
+    uint64_t empty[FA_STAGES];
+    int abort;
+    int pad;
+};
+
+__device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, FaShared* sh, const StepArgs& a, int lane) {
+    volatile int* abort = &sh->abort;
+    for (uint32_t i = 0; i < MBAR_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return *abort == 0;
+        if ((i & 15u) == 15u && *abort) return false;
+    }
+    if (lane == 0) { atomicExch(a.status, STATUS_MBAR_TIMEOUT); atomicExch(&sh->abort, 1); }
+    return false;
+}
+
+// Warps 0..15 compute; warp 16 only issues the bulk copies (a bulk-copy instruction blocks while the copy
+// engine's queue is full, which would otherwise stall a computing warp for about as long as a batch takes).
 template <typename TG, int NG>
-__global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work) {
+__global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work) {
+    constexpr int RBM = NG == 1 ? 16 : (NG == 2 ? 8 : 4);     // most rows a batch can hold for this column count
     extern __shared__ __align__(128) unsigned char smem[];
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
@@ -77,9 +98,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
     const int rb = s.fa_rb;
     const int row_bytes = C * (int)sizeof(TG);
     const int stage_bytes = rb * row_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FA_STAGES * stage_bytes);
-    float* s_part = reinterpret_cast<float*>(bars + FA_STAGES);      // [FA_WARPS][FA_RB_MAX]
-    float* s_w = s_part + FA_WARPS * FA_RB_MAX;                      // [FA_RB_MAX]
+    FaShared* sh = reinterpret_cast<FaShared*>(smem + FA_STAGES * stage_bytes);
+    float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS][FA_RB_MAX], double-buffered by batch
 
     const int strip = w.tile;
     const int row0 = strip * K_TR;
@@ -89,22 +109,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
     const unsigned char* g_src = reinterpret_cast<const unsigned char*>(d.g);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < FA_STAGES; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < FA_STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], FA_WARPS); }
+        sh->abort = 0;
         mbar_init_fence();
     }
     __syncthreads();
 
-    auto issue = [&](int b) {   // warp 0: lane r copies row r of batch b
-        const int rows = min(rb, nrows - b * rb);
-        uint64_t* bar = &bars[b % FA_STAGES];
-        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)rows * (uint32_t)row_bytes);
-        __syncwarp();
-        if (lane < rows)
-            bulk_g2s(smem + (b % FA_STAGES) * stage_bytes + lane * row_bytes,
-                     g_src + (int64_t)(row0 + b * rb + lane) * row_bytes, (uint32_t)row_bytes, bar);
-    };
-    if (warp == 0) {
-        for (int b = 0; b < min(FA_STAGES, nbatch); ++b) issue(b);
+    if (warp == FA_WARPS) {      // producer: lane r copies row r of batch b
+        for (int b = 0; b < nbatch; ++b) {
+            const int slot = b % FA_STAGES;
+            if (b >= FA_STAGES && !fa_wait(&sh->empty[slot], ((b / FA_STAGES) - 1) & 1, sh, a, lane)) return;
+            const int rows = min(rb, nrows - b * rb);
+            if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (uint32_t)row_bytes);
+            __syncwarp();
+            if (lane < rows)
+                bulk_g2s(smem + slot * stage_bytes + lane * row_bytes, g_src + (int64_t)(row0 + b * rb + lane) * row_bytes,
+                         (uint32_t)row_bytes, &sh->full[slot]);
+        }
+        return;
     }
 
     // this thread's column groups: 8 consecutive columns starting at 8 * (threadIdx.x + FA_THREADS * j)
@@ -121,17 +143,19 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
 
     for (int b = 0; b < nbatch; ++b) {
         const int slot = b % FA_STAGES;
-        // uniform result of the bounded wait; also: every thread is done with batch b-1
-        if (!__syncthreads_and(mbar_wait(&bars[slot], (b / FA_STAGES) & 1))) { ok = false; break; }
-        if (warp == 0 && b >= 1 && b + FA_STAGES - 1 < nbatch) issue(b + FA_STAGES - 1);   // into the slot batch b-1 used
+        // After a failed wait a warp keeps walking the batches without touching data, so that it still meets
+        // the other consumer warps at the hardware barrier below once per batch (nobody is left waiting).
+        if (ok && !fa_wait(&sh->full[slot], (b / FA_STAGES) & 1, sh, a, lane)) ok = false;
+        if (!ok) { named_sync(1, FA_THREADS); continue; }
         const int rows = min(rb, nrows - b * rb);
         const unsigned char* st = smem + slot * stage_bytes;
+        float* part = s_part + (b & 1) * (FA_WARPS * FA_RB_MAX);
 
-        // sweep 1: row sums and column sums of g^2.  Row partials of up to FA_RB_MAX rows stay in registers
-        // (static indices: the loops are fully unrolled and guarded) and are reduced across the warp together.
-        float rp[FA_RB_MAX];
+        // sweep 1: row sums and column sums of g^2.  Row partials stay in registers (static indices: the loops
+        // are fully unrolled and guarded) and are reduced across the warp together.
+        float rp[RBM];
 #pragma unroll
-        for (int r = 0; r < FA_RB_MAX; ++r) {
+        for (int r = 0; r < RBM; ++r) {
             rp[r] = 0.0f;
             if (r < rows) {
                 u64 racc = F2ZERO;
@@ -147,42 +171,52 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
                         }
                     }
                 }
-                float lo, hi;
-                upk(racc, lo, hi);
-                rp[r] = lo + hi;
+                rp[r] = racc.x + racc.y;
             }
         }
-        if (rows > 8) {
-            const float t = warp_reduce_rows<16>(rp, lane);
-            if ((lane & 1) == 0) s_part[warp * FA_RB_MAX + ((lane >> 1) & 15)] = t;
-        } else if (rows > 4) {
-            const float t = warp_reduce_rows<8>(rp, lane);
-            if ((lane & 3) == 0) s_part[warp * FA_RB_MAX + ((lane >> 2) & 7)] = t;
+        if (RBM > 8 && rows > 8) {
+            float v16[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) v16[r] = r < RBM ? rp[r] : 0.0f;
+            const float t = warp_reduce_rows<16>(v16, lane);
+            if ((lane & 1) == 0) part[warp * FA_RB_MAX + ((lane >> 1) & 15)] = t;
+        } else if (RBM > 4 && rows > 4) {
+            float v8[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) v8[r] = r < RBM ? rp[r] : 0.0f;
+            const float t = warp_reduce_rows<8>(v8, lane);
+            if ((lane & 3) == 0) part[warp * FA_RB_MAX + ((lane >> 2) & 7)] = t;
         } else {
-            const float t = warp_reduce_rows<4>(rp, lane);
-            if ((lane & 7) == 0) s_part[warp * FA_RB_MAX + ((lane >> 3) & 3)] = t;
+            float v4[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) v4[r] = rp[r];
+            const float t = warp_reduce_rows<4>(v4, lane);
+            if ((lane & 7) == 0) part[warp * FA_RB_MAX + ((lane >> 3) & 3)] = t;
         }
-        __syncthreads();
-        if (warp == 0 && lane < rows) {
+        // barrier among the 16 consumer warps: the per-warp row partials of this batch are complete
+        named_sync(1, FA_THREADS);
+
+        // every warp finishes the row sums itself (lane r: row r), so no second barrier is needed; warp 0
+        // publishes v_row.  Mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the dequantised state.
+        float wrow = 0.0f;
+        if (lane < rows) {
             float sum = 0.0f;
 #pragma unroll
-            for (int ww = 0; ww < FA_WARPS; ++ww) sum += s_part[ww * FA_RB_MAX + lane];
+            for (int ww = 0; ww < FA_WARPS; ++ww) sum += part[ww * FA_RB_MAX + lane];
             const int row = row0 + b * rb + lane;
-            // mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the dequantised old state
             const float mean = (sum + (float)C * h.eps0) / (float)C;
             float old;
             if (quant) old = (float)reinterpret_cast<const uint8_t*>(d.sq_row)[row] * (d.sq_row_absmax[row >> 8] / QMAX_U8);
             else old = reinterpret_cast<const float*>(d.sq_row)[row];
             const float v = old * h.beta2 + h.om_beta2 * mean;
-            s.vr[row] = v;
-            s_w[lane] = v > 0.0f ? 1.0f / v : 0.0f;
+            if (warp == 0) s.vr[row] = v;
+            wrow = v > 0.0f ? 1.0f / v : 0.0f;
         }
-        __syncthreads();
         // sweep 2: column sums of g^2 / v_row
 #pragma unroll
-        for (int r = 0; r < FA_RB_MAX; ++r) {
+        for (int r = 0; r < RBM; ++r) {
             if (r < rows) {
-                const u64 w2 = splat(s_w[r]);
+                const u64 w2 = splat(__shfl_sync(0xffffffffu, wrow, r));
 #pragma unroll
                 for (int j = 0; j < NG; ++j) {
                     if (gvalid[j]) {
@@ -194,28 +228,18 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_sqstat_fused(StepArgs a, cons
                 }
             }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->empty[slot]);
     }
-    if (!ok) {
-        if (threadIdx.x == 0) {
-            atomicExch(a.status, STATUS_MBAR_TIMEOUT);
-            for (int i = 0; i < FA_STAGES; ++i) (void)mbar_wait(&bars[i], 0);
-        }
-        return;
-    }
+    if (!ok) return;      // the status word is set; the partial sums of this strip stay unwritten
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
         if (gvalid[j]) {
             const int64_t off = (int64_t)strip * C + (threadIdx.x + FA_THREADS * j) * 8;
-            float v[8], t[8];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                upk(colb[j][e], v[2 * e], v[2 * e + 1]);
-                upk(colT[j][e], t[2 * e], t[2 * e + 1]);
-            }
-            reinterpret_cast<float4*>(s.colpart + off)[0] = make_float4(v[0], v[1], v[2], v[3]);
-            reinterpret_cast<float4*>(s.colpart + off)[1] = make_float4(v[4], v[5], v[6], v[7]);
-            reinterpret_cast<float4*>(s.tpart + off)[0] = make_float4(t[0], t[1], t[2], t[3]);
-            reinterpret_cast<float4*>(s.tpart + off)[1] = make_float4(t[4], t[5], t[6], t[7]);
+            reinterpret_cast<float4*>(s.colpart + off)[0] = make_float4(colb[j][0].x, colb[j][0].y, colb[j][1].x, colb[j][1].y);
+            reinterpret_cast<float4*>(s.colpart + off)[1] = make_float4(colb[j][2].x, colb[j][2].y, colb[j][3].x, colb[j][3].y);
+            reinterpret_cast<float4*>(s.tpart + off)[0] = make_float4(colT[j][0].x, colT[j][0].y, colT[j][1].x, colT[j][1].y);
+            reinterpret_cast<float4*>(s.tpart + off)[1] = make_float4(colT[j][2].x, colT[j][2].y, colT[j][3].x, colT[j][3].y);
         }
     }
 }
@@ -236,7 +260,7 @@ template <typename TG, int NG>
 static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, size_t smem, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(k_sqstat_fused<TG, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    k_sqstat_fused<TG, NG><<<n, FA_THREADS, smem, st>>>(a, work);
+    k_sqstat_fused<TG, NG><<<n, FA_THREADS + 32, smem, st>>>(a, work);
     return cudaGetLastError();
 }
 
@@ -255,8 +279,7 @@ static cudaError_t launch_ng(int ng, const StepArgs& a, const Work* work, int n,
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_stage_bytes,
                             cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
-    const size_t smem = FA_STAGES * max_stage_bytes + FA_STAGES * sizeof(uint64_t) +
-                        (FA_WARPS * FA_RB_MAX + FA_RB_MAX) * sizeof(float);
+    const size_t smem = FA_STAGES * max_stage_bytes + sizeof(FaShared) + 2 * FA_WARPS * FA_RB_MAX * sizeof(float);
     switch (key.g_dtype) {
         case CAME_DT_F32: return launch_ng<float>(key.mode, a, work, n, smem, st);
         case CAME_DT_F16: return launch_ng<__half>(key.mode, a, work, n, smem, st);
