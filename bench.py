@@ -31,8 +31,8 @@ METRIC = "optimizer-step Gelem/s (CAME8bit, Llama-7B shapes, bf16 p/g)"
 # algorithmic bytes per element of each kernel of the tile-layout step, bf16 p/g (every operand read once,
 # every result written once; absmax adds 4/256 per access)
 KERNEL_BYTES = {
-    "sq_partials": 2.0,                       # g
-    "sumsq": 2.0,                             # g
+    "sq_partials": 2.0,                       # g (fused with the RMS-clip reduction when the row fits on chip)
+    "sumsq": 2.0,                             # g (only for tensors that take the two-pass form)
     "moment": 2.0 + 1.0 + 1.0 + 8.0 / 256,    # g, m read, m write, tile absmax read + write
     "apply": 1.0 + 2.0 + 2.0 + 4.0 / 256,     # m, p read, p write, tile absmax
 }
@@ -305,17 +305,23 @@ def run_gpu(args):
         kernels = {}
         tot = sum(ms for ms, _ in timing.values()) or 1.0
         for name, (ms, n) in timing.items():
-            per = ms / n
-            ent = {"launches": n, "ms_per_launch": per, "share": ms / tot}
+            # a pass may take several launches per step (one per template instance); together they cover every
+            # 2-D element once, so bandwidth is computed per step
+            per_step = ms / args.steps
+            ent = {"launches": n, "launches_per_step": n / args.steps, "ms_per_step": per_step,
+                   "ms_per_launch": ms / n, "share": ms / tot}
             if name in KERNEL_BYTES:
-                gbs = KERNEL_BYTES[name] * owned_2d / (per * 1e-3) / 1e9
+                gbs = KERNEL_BYTES[name] * owned_2d / (per_step * 1e-3) / 1e9
                 ent.update({"alg_bytes_per_elem": KERNEL_BYTES[name], "gbs": gbs, "frac": gbs / peak})
             kernels[name] = ent
         dom = max((k for k in kernels if k in KERNEL_BYTES), key=lambda k: kernels[k]["share"])
         traffic = NCU_TRAFFIC_BYTES_PER_ELEM.get(dom)
+        lps = kernels[dom]["launches_per_step"]
         roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
-                    "frac": kernels[dom]["gbs"] / peak, "traffic": None if traffic is None else traffic * owned_2d,
-                    "peak_source": peak_src, "alg_bytes_per_launch": KERNEL_BYTES[dom] * owned_2d}
+                    "frac": kernels[dom]["gbs"] / peak,
+                    "traffic": None if traffic is None else traffic * owned_2d / lps,
+                    "peak_source": peak_src, "alg_bytes_per_launch": KERNEL_BYTES[dom] * owned_2d / lps,
+                    "ms_per_launch": kernels[dom]["ms_per_launch"], "launches_per_step": lps}
         step_bytes = STEP_BYTES_2D * owned_2d + STEP_BYTES_1D * owned_1d
         step_gbs = step_bytes / (ms_step_only * 1e-3) / 1e9
         line = {

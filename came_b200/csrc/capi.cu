@@ -122,7 +122,7 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.fac = d.mode == CAME_MODE_FLAT8 ? take(2 * (size_t)(g.R + g.C)) : nullptr;
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
-            s.fa_rb = fused_sq_rows_per_batch(g.C * elem_bytes(d.g_dtype));
+            s.fa_rb = fused_sq_rows_per_batch(g.C * elem_bytes(d.g_dtype), g.C);
             s.tpart = take((size_t)g.tiles_r * (size_t)g.C);
         }
     }

@@ -16,6 +16,8 @@
 #include "launch.h"
 #include "pipeline.cuh"
 
+#include <cstdio>
+
 namespace came {
 
 constexpr int FA_THREADS = 512;
@@ -88,7 +90,10 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, FaShared
 // engine's queue is full, which would otherwise stall a computing warp for about as long as a batch takes).
 template <typename TG, int NG>
 __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work) {
-    constexpr int RBM = NG == 1 ? 16 : (NG == 2 ? 8 : 4);     // most rows a batch can hold for this column count
+    // most rows a batch can hold for this column count.  One column group per thread (cols <= 4096): batches are
+    // capped at 4 rows and the squares stay in registers between the two sweeps instead of being re-read.
+    constexpr bool KEEP = NG == 1;
+    constexpr int RBM = NG == 1 ? 4 : (NG == 2 ? 8 : 4);
     extern __shared__ __align__(128) unsigned char smem[];
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
@@ -100,6 +105,7 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     const int stage_bytes = rb * row_bytes;
     FaShared* sh = reinterpret_cast<FaShared*>(smem + FA_STAGES * stage_bytes);
     float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS][FA_RB_MAX], double-buffered by batch
+    float* s_old = s_part + 2 * FA_WARPS * FA_RB_MAX;                // [K_TR] dequantised old v_row of the strip's rows
 
     const int strip = w.tile;
     const int row0 = strip * K_TR;
@@ -112,6 +118,14 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
         for (int i = 0; i < FA_STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], FA_WARPS); }
         sh->abort = 0;
         mbar_init_fence();
+    }
+    // old second-moment state of the strip's rows, fetched once (a dependent global load per batch would sit on
+    // every warp's critical path)
+    if (threadIdx.x < nrows) {
+        const int row = row0 + threadIdx.x;
+        s_old[threadIdx.x] = d.mode != CAME_MODE_FP32
+            ? (float)reinterpret_cast<const uint8_t*>(d.sq_row)[row] * (d.sq_row_absmax[row >> 8] / QMAX_U8)
+            : reinterpret_cast<const float*>(d.sq_row)[row];
     }
     __syncthreads();
 
@@ -138,14 +152,23 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
 #pragma unroll
         for (int e = 0; e < 4; ++e) { colb[j][e] = F2ZERO; colT[j][e] = F2ZERO; }
     }
-    const bool quant = d.mode != CAME_MODE_FP32;
     bool ok = true;
+#ifdef CAME_WIDE_PROFILE
+    long long pf_wait = 0, pf_s1 = 0, pf_bar = 0, pf_fin = 0, pf_s2 = 0;
+    const long long pf_start = clock64();
+#endif
 
     for (int b = 0; b < nbatch; ++b) {
         const int slot = b % FA_STAGES;
         // After a failed wait a warp keeps walking the batches without touching data, so that it still meets
         // the other consumer warps at the hardware barrier below once per batch (nobody is left waiting).
+#ifdef CAME_WIDE_PROFILE
+        const long long c0 = clock64();
+#endif
         if (ok && !fa_wait(&sh->full[slot], (b / FA_STAGES) & 1, sh, a, lane)) ok = false;
+#ifdef CAME_WIDE_PROFILE
+        const long long c1 = clock64();
+#endif
         if (!ok) { named_sync(1, FA_THREADS); continue; }
         const int rows = min(rb, nrows - b * rb);
         const unsigned char* st = smem + slot * stage_bytes;
@@ -154,9 +177,14 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
         // sweep 1: row sums and column sums of g^2.  Row partials stay in registers (static indices: the loops
         // are fully unrolled and guarded) and are reduced across the warp together.
         float rp[RBM];
+        u64 sqk[KEEP ? RBM : 1][4];      // KEEP: g^2 of this thread's elements, reused by sweep 2
 #pragma unroll
         for (int r = 0; r < RBM; ++r) {
             rp[r] = 0.0f;
+            if (KEEP) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sqk[KEEP ? r : 0][e] = F2ZERO;
+            }
             if (r < rows) {
                 u64 racc = F2ZERO;
 #pragma unroll
@@ -166,13 +194,24 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
                         smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            colb[j][e] = fma2(g2[e], g2[e], colb[j][e]);
-                            racc = fma2(g2[e], g2[e], racc);
+                            if (KEEP) {
+                                const u64 sq = mul2(g2[e], g2[e]);
+                                sqk[KEEP ? r : 0][e] = sq;
+                                colb[j][e] = add2(colb[j][e], sq);
+                                racc = add2(racc, sq);
+                            } else {
+                                colb[j][e] = fma2(g2[e], g2[e], colb[j][e]);
+                                racc = fma2(g2[e], g2[e], racc);
+                            }
                         }
                     }
                 }
                 rp[r] = racc.x + racc.y;
             }
+        }
+        if (KEEP) {      // the slot's bytes are in registers: hand it back before the barrier
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->empty[slot]);
         }
         if (RBM > 8 && rows > 8) {
             float v16[16];
@@ -194,7 +233,13 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
             if ((lane & 7) == 0) part[warp * FA_RB_MAX + ((lane >> 3) & 3)] = t;
         }
         // barrier among the 16 consumer warps: the per-warp row partials of this batch are complete
+#ifdef CAME_WIDE_PROFILE
+        const long long c2 = clock64();
+#endif
         named_sync(1, FA_THREADS);
+#ifdef CAME_WIDE_PROFILE
+        const long long c3 = clock64();
+#endif
 
         // every warp finishes the row sums itself (lane r: row r), so no second barrier is needed; warp 0
         // publishes v_row.  Mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the dequantised state.
@@ -205,32 +250,48 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
             for (int ww = 0; ww < FA_WARPS; ++ww) sum += part[ww * FA_RB_MAX + lane];
             const int row = row0 + b * rb + lane;
             const float mean = (sum + (float)C * h.eps0) / (float)C;
-            float old;
-            if (quant) old = (float)reinterpret_cast<const uint8_t*>(d.sq_row)[row] * (d.sq_row_absmax[row >> 8] / QMAX_U8);
-            else old = reinterpret_cast<const float*>(d.sq_row)[row];
-            const float v = old * h.beta2 + h.om_beta2 * mean;
+            const float v = s_old[b * rb + lane] * h.beta2 + h.om_beta2 * mean;
             if (warp == 0) s.vr[row] = v;
             wrow = v > 0.0f ? 1.0f / v : 0.0f;
         }
+#ifdef CAME_WIDE_PROFILE
+        const long long c4 = clock64();
+#endif
         // sweep 2: column sums of g^2 / v_row
 #pragma unroll
         for (int r = 0; r < RBM; ++r) {
             if (r < rows) {
                 const u64 w2 = splat(__shfl_sync(0xffffffffu, wrow, r));
+                if (KEEP) {
 #pragma unroll
-                for (int j = 0; j < NG; ++j) {
-                    if (gvalid[j]) {
-                        u64 g2[4];
-                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
+                    for (int e = 0; e < 4; ++e) colT[0][e] = fma2(sqk[KEEP ? r : 0][e], w2, colT[0][e]);
+                } else {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) colT[j][e] = fma2(mul2(g2[e], g2[e]), w2, colT[j][e]);
+                    for (int j = 0; j < NG; ++j) {
+                        if (gvalid[j]) {
+                            u64 g2[4];
+                            smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) colT[j][e] = fma2(mul2(g2[e], g2[e]), w2, colT[j][e]);
+                        }
                     }
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->empty[slot]);
+        if (!KEEP) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->empty[slot]);
+        }
+#ifdef CAME_WIDE_PROFILE
+        const long long c5 = clock64();
+        pf_wait += c1 - c0; pf_s1 += c2 - c1; pf_bar += c3 - c2; pf_fin += c4 - c3; pf_s2 += c5 - c4;
+#endif
     }
+#ifdef CAME_WIDE_PROFILE
+    if ((blockIdx.x == 0 || blockIdx.x == 200) && lane == 0 && (warp == 0 || warp == 9))
+        printf("sqstat NG %d cta %d warp %d rb %d: total %lld wait %lld sweep1 %lld barrier %lld finalize %lld sweep2 %lld batches %d\n", NG,
+               blockIdx.x, warp, rb, clock64() - pf_start, pf_wait, pf_s1, pf_bar, pf_fin, pf_s2, nbatch);
+#endif
     if (!ok) return;      // the status word is set; the partial sums of this strip stay unwritten
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
@@ -244,10 +305,12 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     }
 }
 
-// rows per staged batch for a row of `row_bytes`: as many as fit 64 KB per slot, at most FA_RB_MAX
-int fused_sq_rows_per_batch(int64_t row_bytes) {
+// rows per staged batch for a row of `row_bytes`: as many as fit 64 KB per slot; at most 4 when a thread owns a
+// single column group (cols <= 4096), else at most 8
+int fused_sq_rows_per_batch(int64_t row_bytes, int64_t cols) {
     int64_t rb = (64 * 1024) / row_bytes;
-    if (rb > FA_RB_MAX) rb = FA_RB_MAX;
+    const int64_t cap = cols <= (int64_t)FA_THREADS * 8 ? 4 : 8;
+    if (rb > cap) rb = cap;
     if (rb < 1) rb = 1;
     return (int)rb;
 }
@@ -279,7 +342,7 @@ static cudaError_t launch_ng(int ng, const StepArgs& a, const Work* work, int n,
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_stage_bytes,
                             cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
-    const size_t smem = FA_STAGES * max_stage_bytes + sizeof(FaShared) + 2 * FA_WARPS * FA_RB_MAX * sizeof(float);
+    const size_t smem = FA_STAGES * max_stage_bytes + sizeof(FaShared) + (2 * FA_WARPS * FA_RB_MAX + K_TR) * sizeof(float);
     switch (key.g_dtype) {
         case CAME_DT_F32: return launch_ng<float>(key.mode, a, work, n, smem, st);
         case CAME_DT_F16: return launch_ng<__half>(key.mode, a, work, n, smem, st);

@@ -45,7 +45,7 @@ cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& 
                               cudaStream_t st);
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_stage_bytes,
                             cudaStream_t st);
-int fused_sq_rows_per_batch(int64_t row_bytes);
+int fused_sq_rows_per_batch(int64_t row_bytes, int64_t cols);
 bool fused_sq_eligible(int64_t cols, int elem_bytes);
 cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                                cudaStream_t st);
