@@ -38,9 +38,10 @@ KERNEL_BYTES = {
 }
 STEP_BYTES_2D = 2.0 + 2.0 + 2.0 + 1.0 + 1.0 + 8.0 / 256    # g, p r/w, m r/w, absmax   = 8.03 B/elem
 STEP_BYTES_1D = 2.0 + 4.0 + 2.0 + 2.0 + 16.0 / 256         # g, p r/w, m r/w, v r/w, two absmax = 10.06 B/elem
-# DRAM bytes per element of the dominant kernel measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum
-# of one launch over a 4096 x 11008 bf16 tensor); None until a capture is committed under profiles/
-NCU_TRAFFIC_BYTES_PER_ELEM = {}
+# DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one launch on the
+# small `--workload profile` case, profiles/tile8_kernels_profile_workload.md); traffic grows in proportion to
+# the element count, so a full launch is this figure times the elements it processes
+NCU_TRAFFIC_BYTES_PER_ELEM = {"sq_partials": 2.05, "moment": 3.97, "apply": 4.79}
 
 
 def llama7b_shapes():
