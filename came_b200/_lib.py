@@ -26,6 +26,7 @@ F_RSQRT_CLAMP = 1 << 8
 
 MAX_GROUPS = 64
 KERNEL_COUNT = 11
+NOALLOC_MAX_ELEMS = 1 << 22
 OK, E_INVALID, E_WORKSPACE, E_CUDA, E_UNSUPPORTED = 0, -1, -2, -3, -4
 
 
@@ -76,6 +77,9 @@ SYMBOLS = {
     "came_b200_plan_set_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "came_b200_plan_read_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "came_b200_kernel_name": (C.c_char_p, [C.c_int]),
+    "came_b200_step_vector_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.POINTER(CameHyper),
+                                                C.c_void_p]),
 }
 
 _lib = None

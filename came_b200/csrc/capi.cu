@@ -193,6 +193,11 @@ Layout layout(const CameTensorDesc* descs, int n) {
 
 }  // namespace
 
+namespace came {
+// lets other translation units leave a message for came_b200_last_error()
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace came
+
 struct came_plan {
     int n_tensors = 0;
     std::vector<CameTensorDesc> descs;

@@ -173,6 +173,25 @@ int came_b200_plan_set_timing(came_plan_t* plan, int enable);
 int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches);
 const char* came_b200_kernel_name(int kernel);
 
+/*
+ * One CAME step on a single 1-D tensor WITHOUT any caller-provided workspace.  This entry point has no
+ * counterpart in the reference.  It exists for hosts that cannot allocate device memory at the point where they
+ * step (the device was handed to the host's own arena at start-up, or the step runs inside a memory plan that
+ * forbids new allocations) and so cannot produce the workspace came_b200_plan_create() needs.  The block sums the
+ * two kernels exchange live in a fixed device array inside the library instead:
+ *   - n <= CAME_B200_NOALLOC_MAX_ELEMS, otherwise CAME_E_UNSUPPORTED;
+ *   - mode is CAME_MODE_FLAT8 (m: int8 codes, v: uint8 codes, both with absmax per 256) or CAME_MODE_FP32
+ *     (m, v: fp32; the absmax pointers are ignored); flags as for a 1-D CameTensorDesc;
+ *   - all calls on a device share that array: calls that overlap on the GPU race, calls on one stream are safe;
+ *   - the first call on a device resolves the array's address; make it outside stream capture;
+ *   - no cudaMalloc, cudaFree or allocating library call is made.
+ * Results are those of came_b200_step() for the same tensor.
+ */
+#define CAME_B200_NOALLOC_MAX_ELEMS (1 << 22)
+int came_b200_step_vector_noalloc(void* p, const void* g, void* m, float* m_absmax, void* v, float* v_absmax,
+                                  int64_t n, int mode, int p_dtype, int g_dtype, uint32_t flags,
+                                  const CameHyper* hyper, came_stream_t stream);
+
 /* error codes */
 #define CAME_OK 0
 #define CAME_E_INVALID (-1)   /* bad argument / descriptor; see came_b200_last_error() */
