@@ -26,7 +26,7 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 HYPER = dict(lr=2e-4, eps=(1e-30, 1e-16), clip_threshold=1.0, betas=(0.9, 0.95, 0.995), weight_decay=1e-2)
-METRIC = "optimizer-step Gelem/s (CAME8bit, Llama-7B shapes, bf16 p/g)"
+METRIC = "optimizer-step Gelem/s (CAME8bit, Llama-7B shapes, bf16 p/g)"   # BASELINE.json: metric
 
 # algorithmic bytes per element of each kernel of the tile-layout step, bf16 p/g (every operand read once,
 # every result written once; absmax adds 4/256 per access)
@@ -66,7 +66,44 @@ def cpu_sample_shapes():
     return [(4096, 4096), (4096, 11008), (11008, 4096), (4096,)]
 
 
-WORKLOADS = {"llama7b": llama7b_shapes, "profile": profile_shapes}
+def gpt2_medium_shapes():
+    """BASELINE config 2: wte 50257x1024, wpe 1024x1024, 24 layers of c_attn 1024x3072, c_proj 1024x1024,
+    c_fc 1024x4096, mlp c_proj 4096x1024 with their biases and two LayerNorms, final LayerNorm (292 tensors)."""
+    shapes = [(50257, 1024), (1024, 1024)]
+    for _ in range(24):
+        shapes += [(1024,), (1024,), (1024, 3072), (3072,), (1024, 1024), (1024,), (1024,), (1024,),
+                   (1024, 4096), (4096,), (4096, 1024), (1024,)]
+    shapes += [(1024,), (1024,)]
+    return shapes
+
+
+def llama1b_shapes():
+    """BASELINE config 4: d=2048, ffn 5632, 22 layers, vocab 32000 (201 tensors, 1 261 529 088 elements)."""
+    shapes = [(32000, 2048)]
+    for _ in range(22):
+        shapes += [(2048, 2048)] * 4 + [(2048, 5632)] * 2 + [(5632, 2048)] + [(2048,)] * 2
+    shapes += [(2048,), (32000, 2048)]
+    return shapes
+
+
+def llama3_8b_shapes():
+    """BASELINE config 5: d=4096, ffn 14336, 32 layers, GQA k/v 4096x1024, vocab 128256 (291 tensors)."""
+    shapes = [(128256, 4096)]
+    for _ in range(32):
+        shapes += [(4096, 4096), (4096, 1024), (4096, 1024), (4096, 4096)] + [(4096, 14336)] * 2 + [(14336, 4096)] + [(4096,)] * 2
+    shapes += [(4096,), (128256, 4096)]
+    return shapes
+
+
+# name -> (shapes, optimizer class, parameter / gradient dtype, betas)
+WORKLOADS = {
+    "llama7b": (llama7b_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
+    "profile": (profile_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
+    "gpt2m_camecuda": (gpt2_medium_shapes, "CAMECUDA", "float32", (0.9, 0.999, 0.9999)),
+    "llama1b_memory": (llama1b_shapes, "CAME8bitMemory", "bfloat16", (0.9, 0.999, 0.9999)),
+    "llama1b_2d": (lambda: [s for s in llama1b_shapes() if len(s) == 2], "CAME8bit2D", "bfloat16", (0.9, 0.999, 0.9999)),
+    "llama3_8b": (llama3_8b_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
+}
 
 
 def peaks():
@@ -208,21 +245,25 @@ def run_gpu(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    shapes = WORKLOADS[args.workload]()
+    shape_fn, cls_name, dtype_name, betas = WORKLOADS[args.workload]
+    shapes = shape_fn()
+    pdtype = getattr(torch, dtype_name)
+    esz = 2 if pdtype != torch.float32 else 4
+    headline = cls_name == "CAME8bit"          # the per-kernel byte table below describes the tile-layout step
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
-    sp = ShardedParams(shapes, torch.bfloat16, dev, world, rank)
+    sp = ShardedParams(shapes, pdtype, dev, world, rank)
     gen = torch.Generator(device=dev).manual_seed(1234)
     # every rank initialises every weight identically (same seed), as after a broadcast at start-up
     for v in sp.views:
-        v.copy_((torch.randn(v.shape, generator=gen, device=dev) * 0.02).to(torch.bfloat16))
+        v.copy_((torch.randn(v.shape, generator=gen, device=dev) * 0.02).to(pdtype))
     params = [torch.nn.Parameter(sp.views[i]) for i in sp.owned]
     ggen = torch.Generator(device=dev).manual_seed(99 + rank)
     scale_gen = torch.Generator().manual_seed(7)
     scales = [10.0 ** float(torch.empty(1).uniform_(-5, -2, generator=scale_gen)) for _ in shapes]
     for p, i in zip(params, sp.owned):
-        p.grad = (torch.randn(p.shape, generator=ggen, device=dev) * scales[i]).to(torch.bfloat16)
-    opt = came_b200.CAME8bit(params, **HYPER)
+        p.grad = (torch.randn(p.shape, generator=ggen, device=dev) * scales[i]).to(pdtype)
+    opt = getattr(came_b200, cls_name)(params, **dict(HYPER, betas=betas))
     owned_elems = sum(numels[i] for i in sp.owned)
     owned_2d = sum(numels[i] for i in sp.owned if len(shapes[i]) == 2)
     owned_1d = owned_elems - owned_2d
@@ -276,10 +317,10 @@ def run_gpu(args):
         key = tuple(p.shape)
         if key not in pinned:
             pinned[key] = p.grad.detach().to("cpu").pin_memory()
-    result_host = torch.empty(4096, dtype=torch.bfloat16).pin_memory()
+    result_host = torch.empty(4096, dtype=pdtype).pin_memory()
     result_src = next(p for p in reversed(params) if p.dim() == 1) if any(p.dim() == 1 for p in params) else params[-1].view(-1)
     h2d_bytes = sum(p.grad.numel() * p.grad.element_size() for p in params)
-    d2h_bytes = min(result_src.numel(), 4096) * 2
+    d2h_bytes = min(result_src.numel(), 4096) * esz
 
     def e2e_step():
         for p in params:
@@ -315,29 +356,40 @@ def run_gpu(args):
                 gbs = KERNEL_BYTES[name] * owned_2d / (per_step * 1e-3) / 1e9
                 ent.update({"alg_bytes_per_elem": KERNEL_BYTES[name], "gbs": gbs, "frac": gbs / peak})
             kernels[name] = ent
-        dom = max((k for k in kernels if k in KERNEL_BYTES), key=lambda k: kernels[k]["share"])
-        traffic = NCU_TRAFFIC_BYTES_PER_ELEM.get(dom)
-        lps = kernels[dom]["launches_per_step"]
-        roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
-                    "frac": kernels[dom]["gbs"] / peak,
-                    "traffic": None if traffic is None else traffic * owned_2d / lps,
-                    "peak_source": peak_src, "alg_bytes_per_launch": KERNEL_BYTES[dom] * owned_2d / lps,
-                    "ms_per_launch": kernels[dom]["ms_per_launch"], "launches_per_step": lps}
-        step_bytes = STEP_BYTES_2D * owned_2d + STEP_BYTES_1D * owned_1d
+        if headline:
+            dom = max((k for k in kernels if k in KERNEL_BYTES), key=lambda k: kernels[k]["share"])
+            traffic = NCU_TRAFFIC_BYTES_PER_ELEM.get(dom)
+            lps = kernels[dom]["launches_per_step"]
+            roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
+                        "frac": kernels[dom]["gbs"] / peak,
+                        "traffic": None if traffic is None else traffic * owned_2d / lps,
+                        "peak_source": peak_src, "alg_bytes_per_launch": KERNEL_BYTES[dom] * owned_2d / lps,
+                        "ms_per_launch": kernels[dom]["ms_per_launch"], "launches_per_step": lps}
+            step_bytes = STEP_BYTES_2D * owned_2d + STEP_BYTES_1D * owned_1d
+        else:
+            # other classes: whole-step algorithmic bytes only (g, p r/w, m r/w; 1-D adds v r/w)
+            for ent in kernels.values():
+                for k in ("alg_bytes_per_elem", "gbs", "frac"):
+                    ent.pop(k, None)
+            msz = 4 if cls_name == "CAMECUDA" else 1
+            step_bytes = (3 * esz + 2 * msz) * owned_2d + (3 * esz + 4 * msz) * owned_1d
+            roofline = None
         step_gbs = step_bytes / (ms_step_only * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": total_elems / (ms_step * 1e-3) / 1e9, "unit": "Gelem/s", "n_gpus": world,
+            "metric": METRIC if args.workload == "llama7b" else f"optimizer-step Gelem/s ({cls_name}, {args.workload})",
+            "value": total_elems / (ms_step * 1e-3) / 1e9, "unit": "Gelem/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded; same gradient "
             "tensors every step; 54 GB touched per step, far above the 126 MB L2)",
-            "config": {"workload": args.workload + "_came8bit_bf16", "tensors": len(shapes), "elements": total_elems,
-                       "state": "int8 exp_avg per 16x16 tile + uint8 row/col vectors (CAME8bit)",
+            "config": {"workload": args.workload, "optimizer": cls_name, "param_dtype": dtype_name,
+                       "tensors": len(shapes), "elements": total_elems,
                        "parallelism": f"ownership x{world} + all-gather" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2"},
             "roofline": roofline,
             "step_roofline": {"alg_bytes_per_step_rank0": step_bytes, "achieved": step_gbs, "peak": peak,
-                              "unit": "GB/s", "frac": step_gbs / peak, "note": "8.03 B/elem (2-D) + 10.06 B/elem (1-D) "
-                              "over the step without the all-gather"},
+                              "unit": "GB/s", "frac": step_gbs / peak, "note": "every operand read once, every result "
+                              "written once (8.03 B/elem for 2-D, 10.06 for 1-D with bf16 p/g and 8-bit states), over the "
+                              "step without the all-gather"},
             "kernels": kernels,
             "gpu_launches": launches,
             "clocks": clocks.summary(),
@@ -367,8 +419,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="llama7b", choices=["llama7b", "profile"],
-                    help="llama7b: the benchmark workload; profile: a small case of the same kernels for ncu")
+    ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
+                    help="llama7b: the benchmark workload (BASELINE config 3); profile: a small case of the same kernels "
+                         "for ncu; the others are BASELINE configs 2, 4 and 5")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
