@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
     }
     const int c8 = lane & 7, rsub = lane >> 3;
     const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
-    const u64 c127 = splat(QMAX_I8), magic = splat(ROUND_MAGIC);
+    const u64 magic = splat(ROUND_MAGIC);
     int q = 0;            // position of the next band to consume in this CTA's band stream
     int buf = 0;
     bool aborted = false;
@@ -379,17 +379,17 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 int8_t* mdst = reinterpret_cast<int8_t*>(d.m) + (int64_t)(brow + rsub) * C + col;
                 // the reciprocal form needs a normal 1/A: decided per warp so that the branch never diverges
                 if (__all_sync(0xffffffffu, recip_safe(A))) {
-                    // code = rint((m / A) * 127) computed as rint((m * (1/A)) * 127): the quotient may differ from
-                    // the IEEE one in its last bit, which moves a code only when (m/A)*127 lies within ~1e-5 of a
-                    // rounding boundary (the reference kernel multiplies by a reciprocal as well,
-                    // came_kernels.cu:833-836).  The product and the rounding constant go through one FMA; the
-                    // sum's low mantissa byte is the two's-complement code.
-                    const u64 inv2 = splat(1.0f / A);
+                    // code = rint((m / A) * 127) computed as rint(m * (127 / A)) in one FMA with the rounding constant:
+                    // the argument may differ from the two-step IEEE value in its last bits, which moves a code only
+                    // when it lies within ~1e-5 of a rounding boundary (the reference kernel multiplies by a
+                    // reciprocal as well, came_kernels.cu:833-836).  The sum's low mantissa byte is the
+                    // two's-complement code.
+                    const u64 s127 = splat(QMAX_I8 / A);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         u64 y[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) y[j] = fma2(mul2(m2[i][j], inv2), c127, magic);
+                        for (int j = 0; j < 4; ++j) y[j] = fma2(m2[i][j], s127, magic);
                         if (FULL || brow + rsub + 4 * i < R)
                             *reinterpret_cast<uint2*>(mdst + (int64_t)(4 * i) * C) = make_uint2(pack_codes4(y[0], y[1]), pack_codes4(y[2], y[3]));
                     }
@@ -516,8 +516,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
         for (int j = 0; j < 4; ++j) cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
         const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
         float a_next = active ? amax_col[0] : 0.0f;     // tile absmax, fetched one band ahead
-        const bool decay = h.weight_decay != 0.0f;
-        const int wd_form = (d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 1 : 0);
+        const int wd_mode = h.weight_decay == 0.0f ? 0 : ((d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 3 : 1));
         const u64 dmul2 = splat(h.decay_mul), nwdlr2 = splat(-h.wd_lr), nlr2 = splat(-h.lr);
         bool ok = true;
 
@@ -533,35 +532,49 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
             const float A = a_next;
             if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
             const float scl = A > 0.0f ? A / QMAX_I8 : 0.0f;
-            u64 p2[4][4];
-            uint2 mv[4];
+            // WD: 0 no decay, 1 one rounding, 2 multiply form with a rounding, 3 add form with a rounding.
+            // FULL: all 16 rows of the band exist.  Both are uniform over the item, so the inner loops carry no
+            // branches.
+            auto band = [&](auto wd_tag, auto full_tag) {
+                constexpr int WD = decltype(wd_tag)::value;
+                constexpr bool FULL = decltype(full_tag)::value;
+                u64 p2[4][4];
+                uint2 mv[4];
+                float rfac[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = rsub + 4 * i;
-                wide_run8(reinterpret_cast<const TP*>(sp + r * ROW), p2[i]);
-                mv[i] = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
-            }
-            float rfac[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) rfac[i] = sr[k * W_BAND + rsub + 4 * i];
-            wide_release(sh, slot, lane);
-            TP* pdst = reinterpret_cast<TP*>(d.p) + (int64_t)(brow + rsub) * C + col;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t mx = mv[i].x ^ 0x80808080u, my = mv[i].y ^ 0x80808080u;
-                const u64 scr2 = splat(scl * rfac[i]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const u64 upd = mul2(mul2(codes_to_f2(j < 2 ? mx : my, (j & 1) * 2), scr2), cf2[j]);
-                    u64 pv = p2[i][j];
-                    if (decay) {
-                        if (wd_form == 2) pv = round_pair<TP>(mul2(pv, dmul2));
-                        else if (wd_form == 1) pv = round_pair<TP>(fma2(nwdlr2, pv, pv));
-                        else pv = fma2(nwdlr2, pv, pv);
-                    }
-                    p2[i][j] = fma2(nlr2, upd, pv);
+                for (int i = 0; i < 4; ++i) {
+                    const int r = rsub + 4 * i;
+                    wide_run8(reinterpret_cast<const TP*>(sp + r * ROW), p2[i]);
+                    mv[i] = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
+                    rfac[i] = sr[k * W_BAND + r];
                 }
-                if (full_band || brow + rsub + 4 * i < R) wide_store8(pdst + (int64_t)(4 * i) * C, p2[i]);
+                wide_release(sh, slot, lane);
+                TP* pdst = reinterpret_cast<TP*>(d.p) + (int64_t)(brow + rsub) * C + col;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t mx = mv[i].x ^ 0x80808080u, my = mv[i].y ^ 0x80808080u;
+                    const u64 scr2 = splat(scl * rfac[i]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const u64 upd = mul2(mul2(codes_to_f2(j < 2 ? mx : my, (j & 1) * 2), scr2), cf2[j]);
+                        u64 pv = p2[i][j];
+                        if (WD == 2) pv = round_pair<TP>(mul2(pv, dmul2));
+                        else if (WD == 3) pv = round_pair<TP>(fma2(nwdlr2, pv, pv));
+                        else if (WD == 1) pv = fma2(nwdlr2, pv, pv);
+                        p2[i][j] = fma2(nlr2, upd, pv);
+                    }
+                    if (FULL || brow + rsub + 4 * i < R) wide_store8(pdst + (int64_t)(4 * i) * C, p2[i]);
+                }
+            };
+            auto band_wd = [&](auto wd_tag) {
+                if (full_band) band(wd_tag, std::true_type{});
+                else band(wd_tag, std::false_type{});
+            };
+            switch (wd_mode) {
+                case 0: band_wd(std::integral_constant<int, 0>{}); break;
+                case 1: band_wd(std::integral_constant<int, 1>{}); break;
+                case 2: band_wd(std::integral_constant<int, 2>{}); break;
+                default: band_wd(std::integral_constant<int, 3>{}); break;
             }
         }
         if (!ok) { aborted = true; continue; }

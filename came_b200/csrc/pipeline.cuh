@@ -62,10 +62,17 @@ __device__ __forceinline__ u64 pk(float lo, float hi) { return make_float2(lo, h
 __device__ __forceinline__ u64 pk_u32(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
 __device__ __forceinline__ void upk(u64 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
 __device__ __forceinline__ void upk_u32(u64 v, uint32_t& lo, uint32_t& hi) { lo = __float_as_uint(v.x); hi = __float_as_uint(v.y); }
+#ifdef CAME_SCALAR_FP32   // build-time experiment: the same arithmetic with scalar instructions
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) { return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y)); }
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ u64 add2(u64 a, u64 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) { return make_float2(__fsub_rn(a.x, b.x), __fsub_rn(a.y, b.y)); }
+#else
 __device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ u64 mul2(u64 a, u64 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ u64 add2(u64 a, u64 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ u64 sub2(u64 a, u64 b) { return __fadd2_rn(a, make_float2(-b.x, -b.y)); }
+#endif
 __device__ __forceinline__ u64 splat(float x) { return make_float2(x, x); }
 
 // two int8 codes (bytes `b`, `b+1` of the word `x`, already biased by ^0x80) -> packed exact floats:
