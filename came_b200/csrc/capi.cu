@@ -120,6 +120,7 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.colpart = take((size_t)std::max(g.tiles_r, g.ptiles_r) * (size_t)g.C);
         s.spart = take(std::max((size_t)g.tiles_r * (size_t)g.tiles_c, (size_t)g.nbC));
         s.fac = d.mode == CAME_MODE_FLAT8 ? take(2 * (size_t)(g.R + g.C)) : nullptr;
+        if (vec_flags(d).p2 == 2) s.res_eps_deferred = 1;
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
             s.fa_rb = fused_sq_rows_per_batch(g.C * elem_bytes(d.g_dtype), g.C);

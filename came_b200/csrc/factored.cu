@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
             if (!is_col) {
                 const int parts = RES ? s.ptiles_c : s.tiles_c;
                 for (int t = 0; t < parts; ++t) acc += s.rowpart[(int64_t)t * R + idx];
+                if (RES && s.res_eps_deferred) acc += (float)C * h.eps1;
                 acc = acc / (float)C;
             } else {
                 const int parts = RES ? s.ptiles_r : s.tiles_r;
@@ -142,6 +143,7 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
                     acc += (float)R * h.eps0;
                     for (int t = 0; t < parts; ++t) tsum += s.tpart[(int64_t)t * C + idx];
                 }
+                if (RES && s.res_eps_deferred) acc += (float)R * h.eps1;
                 acc = acc / (float)R;
             }
             float old;

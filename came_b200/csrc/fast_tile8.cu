@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         // on the critical path of the iteration
         const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
         float a_next = active ? amax_col[0] : 0.0f;
-        const u64 om2 = splat(h.om_beta1), eps2 = splat(h.eps1);
+        const u64 om2 = splat(h.om_beta1);
         const float beta1 = h.beta1;
         bool ok = true;
 
@@ -360,11 +360,11 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                         const u64 u2 = mul2(mul2(g2[j], ra2), cf2[j]);
                         const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scb2);
                         u64 mn = fma2(om2, u2, mo2);
-                        const u64 df2 = sub2(u2, mn);
-                        u64 res2 = fma2(df2, df2, eps2);
-                        if (!FULL && !live) { res2 = F2ZERO; mn = F2ZERO; }
-                        colacc[j] = add2(colacc[j], res2);
-                        rs2 = add2(rs2, res2);
+                        u64 df2 = sub2(u2, mn);
+                        if (!FULL && !live) { df2 = F2ZERO; mn = F2ZERO; }
+                        // sums of (u - m)^2; eps1 is added once per row / column when the partials are finalised
+                        colacc[j] = fma2(df2, df2, colacc[j]);
+                        rs2 = fma2(df2, df2, rs2);
                         amax = fmaxf(amax, fmaxf(fabsf(mn.x), fabsf(mn.y)));
                         m2[i][j] = mn;
                     }
