@@ -231,7 +231,7 @@ def run_reference(args):
 def run_gpu(args):
     import torch.distributed as dist
     import came_b200
-    from came_b200.partition import ShardedParams, imbalance
+    from came_b200.partition import ShardedParams, ShardedStepper, imbalance
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -252,7 +252,8 @@ def run_gpu(args):
     headline = cls_name == "CAME8bit"          # the per-kernel byte table below describes the tile-layout step
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
-    sp = ShardedParams(shapes, pdtype, dev, world, rank)
+    n_buckets = args.buckets if args.buckets > 0 else (4 if world > 1 else 1)
+    sp = ShardedParams(shapes, pdtype, dev, world, rank, buckets=n_buckets)
     gen = torch.Generator(device=dev).manual_seed(1234)
     # every rank initialises every weight identically (same seed), as after a broadcast at start-up
     for v in sp.views:
@@ -263,14 +264,14 @@ def run_gpu(args):
     scales = [10.0 ** float(torch.empty(1).uniform_(-5, -2, generator=scale_gen)) for _ in shapes]
     for p, i in zip(params, sp.owned):
         p.grad = (torch.randn(p.shape, generator=ggen, device=dev) * scales[i]).to(pdtype)
-    opt = getattr(came_b200, cls_name)(params, **dict(HYPER, betas=betas))
+    by_index = dict(zip(sp.owned, params))
+    stepper = ShardedStepper(sp, by_index, lambda ps: getattr(came_b200, cls_name)(ps, **dict(HYPER, betas=betas)))
     owned_elems = sum(numels[i] for i in sp.owned)
     owned_2d = sum(numels[i] for i in sp.owned if len(shapes[i]) == 2)
     owned_1d = owned_elems - owned_2d
 
     def step():
-        opt.step()
-        sp.all_gather()
+        stepper.step()      # buckets: step b, then its all-gather runs while bucket b+1 is stepped
 
     def barrier():
         if world > 1:
@@ -280,35 +281,39 @@ def run_gpu(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    plan = opt._engine.plans[dev]
-    plan.set_timing(True)
+    plans = [o._engine.plans[dev] for o in stepper.opts if o is not None]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ag_events = []
-    with ClockSampler(physical_gpu_index(local)) as clocks:
+
+    def timed(fn, n):
         barrier()
         e0.record()
-        for _ in range(args.steps):
-            opt.step()
-            if world > 1:
-                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a0.record()
-                sp.all_gather()
-                a1.record()
-                ag_events.append((a0, a1))
+        for _ in range(n):
+            fn()
         e1.record()
         barrier()
-    ms_total = e0.elapsed_time(e1)
-    timing = plan.read_timing()
-    plan.set_timing(False)
-    launches = opt.last_step_launches * args.steps
-    ag_ms = sum(a.elapsed_time(b) for a, b in ag_events) / max(len(ag_events), 1)
+        return e0.elapsed_time(e1)
 
-    t = torch.tensor([ms_total, ms_total - ag_ms * args.steps, ag_ms], device=dev, dtype=torch.float64)
+    # separate legs (multi-GPU only): the step without the gather, and the gather alone
+    ms_step_only_total = timed(lambda: stepper.step(gather=False), args.steps) if world > 1 else 0.0
+    ms_ag_total = timed(lambda: [w.wait() for w in sp.all_gather(async_op=True)], args.steps) if world > 1 else 0.0
+    for plan in plans:
+        plan.set_timing(True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        ms_total = timed(step, args.steps)
+    timing = {}
+    for plan in plans:
+        for name, (ms, n) in plan.read_timing().items():
+            a_ms, a_n = timing.get(name, (0.0, 0))
+            timing[name] = (a_ms + ms, a_n + n)
+        plan.set_timing(False)
+    launches = stepper.last_step_launches * args.steps
+
+    t = torch.tensor([ms_total, ms_step_only_total, ms_ag_total], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t[0]) / args.steps
-    ms_step_only = float(t[1]) / args.steps
-    ag_ms = float(t[2])
+    ms_step_only = float(t[1]) / args.steps if world > 1 else ms_step
+    ag_ms = float(t[2]) / args.steps
 
     # ---- end to end through the public API with host buffers (rank-local; max over ranks) -------------
     e2e_steps = min(args.steps, 5)
@@ -325,8 +330,7 @@ def run_gpu(args):
     def e2e_step():
         for p in params:
             p.grad.copy_(pinned[tuple(p.shape)], non_blocking=True)      # this step's gradients: host -> device
-        opt.step()
-        sp.all_gather()
+        stepper.step()
         result_host[: min(result_src.numel(), 4096)].copy_(result_src.data.view(-1)[:4096], non_blocking=True)
 
     e2e_step()
@@ -383,7 +387,8 @@ def run_gpu(args):
             "tensors every step; 54 GB touched per step, far above the 126 MB L2)",
             "config": {"workload": args.workload, "optimizer": cls_name, "param_dtype": dtype_name,
                        "tensors": len(shapes), "elements": total_elems,
-                       "parallelism": f"ownership x{world} + all-gather" if world > 1 else "single GPU",
+                       "parallelism": f"ownership x{world}, {n_buckets} buckets, all-gather of bucket b overlapped with the "
+                                      f"step of bucket b+1" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2"},
             "roofline": roofline,
             "step_roofline": {"alg_bytes_per_step_rank0": step_bytes, "achieved": step_gbs, "peak": peak,
@@ -398,6 +403,7 @@ def run_gpu(args):
         }
         if world > 1:
             line["multi_gpu"] = {
+                "note": "value / ms_per_step time the overlapped step + all-gather; the two legs below are timed alone",
                 "step_only_ms": ms_step_only, "step_only_gelem_s": total_elems / (ms_step_only * 1e-3) / 1e9,
                 "all_gather_ms": ag_ms, "all_gather_gbs_in": sp.gathered_bytes_per_rank() / (ag_ms * 1e-3) / 1e9,
                 "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world)}
@@ -419,6 +425,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--buckets", type=int, default=0, help="all-gather buckets at N > 1 (0: 4 when N > 1, else 1)")
     ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
                     help="llama7b: the benchmark workload (BASELINE config 3); profile: a small case of the same kernels "
                          "for ncu; the others are BASELINE configs 2, 4 and 5")

@@ -43,38 +43,93 @@ def imbalance(numels, owners, world_size: int) -> float:
 
 
 class ShardedParams:
-    """All parameters of a model as views into one flat buffer laid out for an in-place all-gather."""
+    """All parameters of a model as views into one flat buffer laid out for in-place all-gathers.
 
-    def __init__(self, shapes, dtype: torch.dtype, device, world_size: int, rank: int, owners=None):
+    Layout: [bucket][owner rank][that rank's tensors of the bucket, padded to the bucket's piece length].
+    With one bucket this is the plain "slice per owner" layout.  With several, bucket b of every rank can be
+    gathered (one contiguous in-place all-gather) while the ranks are still stepping bucket b+1."""
+
+    def __init__(self, shapes, dtype: torch.dtype, device, world_size: int, rank: int, owners=None, buckets: int = 1):
         self.shapes = [tuple(s) for s in shapes]
         self.world_size, self.rank = int(world_size), int(rank)
+        self.n_buckets = max(1, int(buckets))
         numels = [math.prod(s) for s in self.shapes]
         self.owners = list(owners) if owners is not None else assign_owners(numels, world_size)
         if len(self.owners) != len(self.shapes) or any(not 0 <= r < world_size for r in self.owners):
             raise ValueError("owners must give one rank in [0, world_size) per tensor")
-        # offsets inside each owner's slice
-        fill = [0] * world_size
+        # inside each rank: spread its tensors over the buckets, again greedily by size
+        self.bucket_of = [0] * len(self.shapes)
+        for r in range(world_size):
+            mine = [i for i, o in enumerate(self.owners) if o == r]
+            sub = assign_owners([numels[i] for i in mine], self.n_buckets)
+            for i, b in zip(mine, sub):
+                self.bucket_of[i] = b
+        # offsets inside each (bucket, rank) cell
+        fill = [[0] * world_size for _ in range(self.n_buckets)]
         local_off = []
-        for n, r in zip(numels, self.owners):
-            local_off.append(fill[r])
-            fill[r] += (n + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
-        self.slice_len = max(max(fill), ALIGN_ELEMS)
-        self.flat = torch.zeros(self.slice_len * world_size, dtype=dtype, device=device)
+        for n, r, b in zip(numels, self.owners, self.bucket_of):
+            local_off.append(fill[b][r])
+            fill[b][r] += (n + ALIGN_ELEMS - 1) // ALIGN_ELEMS * ALIGN_ELEMS
+        self.piece_len = [max(max(fill[b]), ALIGN_ELEMS) for b in range(self.n_buckets)]
+        self.bucket_off = [0]
+        for b in range(self.n_buckets):
+            self.bucket_off.append(self.bucket_off[-1] + self.piece_len[b] * world_size)
+        self.slice_len = sum(self.piece_len)          # elements each rank contributes over all buckets
+        self.flat = torch.zeros(self.bucket_off[-1], dtype=dtype, device=device)
         self.views = []
-        for shape, n, r, off in zip(self.shapes, numels, self.owners, local_off):
-            start = r * self.slice_len + off
+        for shape, n, r, b, off in zip(self.shapes, numels, self.owners, self.bucket_of, local_off):
+            start = self.bucket_off[b] + r * self.piece_len[b] + off
             self.views.append(self.flat[start:start + n].view(shape))
         self.owned = [i for i, r in enumerate(self.owners) if r == rank]
 
-    def my_slice(self) -> torch.Tensor:
-        return self.flat[self.rank * self.slice_len:(self.rank + 1) * self.slice_len]
+    def owned_in_bucket(self, b: int):
+        return [i for i in self.owned if self.bucket_of[i] == b]
 
-    def all_gather(self, group=None, async_op: bool = False):
-        """Every rank sends its slice and receives everybody else's, in place."""
+    def bucket_region(self, b: int) -> torch.Tensor:
+        return self.flat[self.bucket_off[b]:self.bucket_off[b + 1]]
+
+    def my_piece(self, b: int) -> torch.Tensor:
+        start = self.bucket_off[b] + self.rank * self.piece_len[b]
+        return self.flat[start:start + self.piece_len[b]]
+
+    def all_gather_bucket(self, b: int, group=None, async_op: bool = False):
+        """Every rank sends its piece of bucket b and receives everybody else's, in place."""
         if self.world_size == 1:
             return None
-        return dist.all_gather_into_tensor(self.flat, self.my_slice(), group=group, async_op=async_op)
+        return dist.all_gather_into_tensor(self.bucket_region(b), self.my_piece(b), group=group, async_op=async_op)
+
+    def all_gather(self, group=None, async_op: bool = False):
+        """Gathers every bucket; with async_op returns the list of work handles."""
+        works = [self.all_gather_bucket(b, group=group, async_op=async_op) for b in range(self.n_buckets)]
+        return works if async_op else None
 
     def gathered_bytes_per_rank(self) -> int:
-        """Bytes each rank receives from its peers in one all-gather."""
+        """Bytes each rank receives from its peers in one full all-gather."""
         return (self.world_size - 1) * self.slice_len * self.flat.element_size()
+
+
+class ShardedStepper:
+    """One optimizer per bucket over the tensors this rank owns; `step()` steps bucket after bucket and starts the
+    all-gather of a bucket's updated weights as soon as its step kernels are enqueued, so that the gather of
+    bucket b travels over NVLink while bucket b+1 is being stepped."""
+
+    def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer):
+        self.sharded = sharded
+        self.opts = []
+        for b in range(sharded.n_buckets):
+            ps = [params_by_index[i] for i in sharded.owned_in_bucket(b)]
+            self.opts.append(make_optimizer(ps) if ps else None)
+
+    def step(self, gather: bool = True):
+        works = []
+        for b, opt in enumerate(self.opts):
+            if opt is not None:
+                opt.step()
+            if gather and self.sharded.world_size > 1:
+                works.append(self.sharded.all_gather_bucket(b, async_op=True))
+        for w in works:
+            w.wait()
+
+    @property
+    def last_step_launches(self) -> int:
+        return sum(o.last_step_launches for o in self.opts if o is not None)

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from came_b200.partition import ShardedParams, assign_owners, imbalance
+from came_b200.partition import ShardedParams, ShardedStepper, assign_owners, imbalance
 
 SHAPES = [(64, 48), (300,), (33, 17), (128, 256), (40,), (96, 64), (16, 16)]
 
@@ -40,6 +40,20 @@ def test_views_alias_flat_buffer_and_are_aligned():
     assert sorted(sp.owned) == [i for i, r in enumerate(sp.owners) if r == 1]
 
 
+def test_bucketed_layout_keeps_cells_contiguous():
+    sp = ShardedParams(SHAPES, torch.float32, "cpu", world_size=2, rank=0, buckets=3)
+    assert len(sp.piece_len) == 3 and sp.flat.numel() == 2 * sum(sp.piece_len)
+    seen = torch.zeros(sp.flat.numel(), dtype=torch.int32)
+    for i, v in enumerate(sp.views):
+        off = (v.data_ptr() - sp.flat.data_ptr()) // 4
+        b, r = sp.bucket_of[i], sp.owners[i]
+        lo = sp.bucket_off[b] + r * sp.piece_len[b]
+        assert lo <= off and off + v.numel() <= lo + sp.piece_len[b]
+        seen[off:off + v.numel()] += 1
+    assert int(seen.max()) == 1
+    assert sorted(i for b in range(3) for i in sp.owned_in_bucket(b)) == sorted(sp.owned)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -55,14 +69,24 @@ def _worker(rank, world, port, out_dir):
         torch.manual_seed(0)
         init = [torch.randn(s) * 0.02 for s in SHAPES]
         grads = [torch.randn(s) * 1e-3 for s in SHAPES]
-        sp = ShardedParams(SHAPES, torch.float32, "cpu", world, rank)
+        sp = ShardedParams(SHAPES, torch.float32, "cpu", world, rank, buckets=3)
         for v, x in zip(sp.views, init):
             v.copy_(x)
         hp = orc.Hyper(weight_decay=1e-2)
-        for i in sp.owned:                      # each rank steps only the tensors it owns
-            st = orc.init_state(sp.views[i], orc.CUDAFP)
-            sp.views[i].copy_(orc.step(sp.views[i].clone(), grads[i], st, hp, orc.CUDAFP))
-        sp.all_gather()
+
+        class OracleOptimizer:      # stands in for a came_b200 class on CPU ranks: steps the tensors it is given
+            last_step_launches = 0
+
+            def __init__(self, idx):
+                self.idx = idx
+
+            def step(self):
+                for i in self.idx:
+                    st = orc.init_state(sp.views[i], orc.CUDAFP)
+                    sp.views[i].copy_(orc.step(sp.views[i].clone(), grads[i], st, hp, orc.CUDAFP))
+
+        # each rank steps only the tensors it owns, bucket by bucket, gathering each bucket as it is done
+        ShardedStepper(sp, {i: i for i in sp.owned}, OracleOptimizer).step()
         torch.save([v.clone() for v in sp.views], os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
