@@ -60,13 +60,16 @@ VecFlags vec_flags(const CameTensorDesc& d) {
     if (d.cols == 0) return v;
     const bool c8 = d.cols % 8 == 0, c16 = d.cols % 16 == 0;
     // staged fast path of the momentum / apply passes: both or neither, as they share the tile geometry
-    const bool fast = d.mode == CAME_MODE_TILE8 && d.cols % 64 == 0 && !g_disable_fast && aligned16(d.g) &&
-                      aligned16(d.m) && aligned16(d.p);
+    const bool all_aligned = aligned16(d.g) && aligned16(d.m) && aligned16(d.p);
+    const bool fast = !g_disable_fast && all_aligned &&
+                      ((d.mode == CAME_MODE_TILE8 && d.cols % 64 == 0) ||
+                       (d.mode == CAME_MODE_FLAT8 && d.cols % 256 == 0 && d.g_dtype == d.p_dtype));
     v.k = c8 && aligned16(d.g);
     if (v.k && !g_disable_fast && !(d.flags & CAME_F_SQ_CLAMP) && fused_sq_eligible(d.cols, elem_bytes(d.g_dtype))) v.k = 2;
     v.p2 = (c16 && aligned16(d.g) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.p3 = (c16 && aligned16(d.p) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.flat = c8 && aligned16(d.g) && aligned16(d.p) && (reinterpret_cast<uintptr_t>(d.m) & 7u) == 0;
+    if (fast && d.mode == CAME_MODE_FLAT8) v.flat = 2;
     return v;
 }
 
@@ -119,7 +122,7 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.rowpart = take((size_t)std::max(g.tiles_c, g.ptiles_c) * (size_t)g.R);
         s.colpart = take((size_t)std::max(g.tiles_r, g.ptiles_r) * (size_t)g.C);
         s.spart = take(std::max((size_t)g.tiles_r * (size_t)g.tiles_c, (size_t)g.nbC));
-        s.fac = d.mode == CAME_MODE_FLAT8 ? take(2 * (size_t)(g.R + g.C)) : nullptr;
+        s.fac = (d.mode == CAME_MODE_FLAT8 && vec_flags(d).flat != 2) ? take(2 * (size_t)(g.R + g.C)) : nullptr;
         if (vec_flags(d).p2 == 2) s.res_eps_deferred = 1;
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
@@ -169,7 +172,8 @@ size_t count_work(const CameTensorDesc* descs, int n) {
         w += 2 * (size_t)(g.nbR + g.nbC);            // two vector finalizes
         w += 1;                                      // s_finalize
         w += (size_t)g.ptiles_r * g.ptiles_c;        // moment
-        if (descs[i].mode == CAME_MODE_FLAT8) w += (size_t)(g.nbR + g.nbC) + (size_t)g.flat_chunks;
+        if (descs[i].mode == CAME_MODE_FLAT8)
+            w += (size_t)(g.nbR + g.nbC) + std::max((size_t)g.flat_chunks, (size_t)g.ptiles_r * g.ptiles_c);
         else w += (size_t)g.ptiles_r * g.ptiles_c;   // apply
     }
     return w;
@@ -336,9 +340,13 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_RES_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
     build(KID_APPLY, notflat, [&](int i) { return Key{0, D[i].p_dtype, D[i].mode, vf[i].p3}; },
           [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
-    build(KID_FACTORS, isflat, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
-    build(KID_APPLY_FLAT, isflat, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, vf[i].flat}; },
+    auto flat_generic = [&](int i) { return isflat(i) && vf[i].flat != 2; };
+    auto flat_staged = [&](int i) { return isflat(i) && vf[i].flat == 2; };
+    build(KID_FACTORS, flat_generic, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
+    build(KID_APPLY_FLAT, flat_generic, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, vf[i].flat}; },
           [&](int i) { return geo[i].flat_chunks; });
+    build(KID_APPLY_FLAT, flat_staged, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 2}; },
+          [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
 
     if (work.size() > L.n_work) {
         delete plan;

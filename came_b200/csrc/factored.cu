@@ -615,7 +615,9 @@ cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a,
             if (key.variant == 2) return launch_fast_tile8(kernel, key, a, work, n, st);
             return go(pick_apply(key.p_dtype, key.mode, (key.variant >= 1)), a, work, n, st);
         case KID_FACTORS: return go(k_factors, a, work, n, st);
-        case KID_APPLY_FLAT: return go(pick_apply_flat(key.g_dtype, key.p_dtype, (key.variant >= 1)), a, work, n, st);
+        case KID_APPLY_FLAT:
+            if (key.variant == 2) return launch_fast_tile8(kernel, key, a, work, n, st);
+            return go(pick_apply_flat(key.g_dtype, key.p_dtype, (key.variant >= 1)), a, work, n, st);
         default: return cudaErrorInvalidValue;
     }
 }

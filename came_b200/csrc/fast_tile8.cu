@@ -225,7 +225,11 @@ __device__ __forceinline__ float warp_vector_sum(const float* x, int n, int lane
 // ------------------------------------------------------------------------------------------------
 // momentum pass (reference: kUpdateExpAvgQuantAndResSumsTiled came_kernels.cu:2584-2683)
 // ------------------------------------------------------------------------------------------------
-template <typename TG>
+// FLAT = false: tile layout, the momentum is re-quantised and written here.  FLAT = true: flat layout (absmax per
+// 256 consecutive elements = per 256-column row segment, the column count being a multiple of 256): only the
+// residual sums are produced; the flat apply pass recomputes the momentum so that its un-quantised value feeds
+// the update (came_kernels.cu:2246-2305 keeps it in fp32 scratch instead).
+template <typename TG, bool FLAT>
 __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
     constexpr int STAGES = WideCfg<TG>::STAGES, STAGE = WideCfg<TG>::STAGE, ROW = WideCfg<TG>::ROW;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -311,7 +315,16 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         // old tile absmax, fetched one band ahead: a dependent global load at the top of every band would sit
         // on the critical path of the iteration
         const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
-        float a_next = active ? amax_col[0] : 0.0f;
+        float a_next = (active && !FLAT) ? amax_col[0] : 0.0f;
+        // flat layout: one absmax per (row, 256-column segment); this lane's 4 rows of the band, one band ahead
+        const float* amax_flat = d.m_absmax + (((int64_t)(it.row0 + rsub) * C + col) >> 8);
+        const int64_t flat_row_step = C >> 8;       // absmax entries per row
+        float af_next[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (FLAT && active) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (it.row0 + rsub + 4 * i < R) af_next[i] = amax_flat[(int64_t)(4 * i) * flat_row_step];
+        }
         const u64 om2 = splat(h.om_beta1);
         const float beta1 = h.beta1;
         bool ok = true;
@@ -333,11 +346,20 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             const int brow = it.row0 + k * W_BAND;
             const int64_t tile_id = (int64_t)(brow >> 4) * tile_cols + (col >> 4);
             const float a_old = a_next;
-            if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
+            if (!FLAT && k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
             const u64 scb2 = splat(a_old > 0.0f ? (a_old / QMAX_I8) * beta1 : 0.0f);
+            float af[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) af[i] = af_next[i];
+            if (FLAT && k + 1 < it.nbands) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (brow + W_BAND + rsub + 4 * i < R)
+                        af_next[i] = amax_flat[(int64_t)((k + 1) * W_BAND + 4 * i) * flat_row_step];
+            }
             const bool full_band = brow + W_BAND <= R;     // uniform over the CTA
             float rsum[4];
-            float A;
+            float A = 1.0f;
             // FULL: all 16 rows of the band exist: no per-row predicate anywhere.  Otherwise (only the last band
             // of a matrix whose row count is not a multiple of 16) rows past the end hold stale bytes in shared
             // memory; whatever they produce is kept out of the sums, the absmax and the stores.
@@ -354,23 +376,27 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                     uint2 mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
                     mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
                     const u64 ra2 = splat(live ? sr[k * W_BAND + r] : 0.0f);
+                    const u64 sc_row2 = FLAT ? splat((af[i] / QMAX_I8) * beta1) : scb2;
                     u64 rs2 = F2ZERO;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const u64 u2 = mul2(mul2(g2[j], ra2), cf2[j]);
-                        const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scb2);
+                        const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), sc_row2);
                         u64 mn = fma2(om2, u2, mo2);
                         u64 df2 = sub2(u2, mn);
                         if (!FULL && !live) { df2 = F2ZERO; mn = F2ZERO; }
                         // sums of (u - m)^2; eps1 is added once per row / column when the partials are finalised
                         colacc[j] = fma2(df2, df2, colacc[j]);
                         rs2 = fma2(df2, df2, rs2);
-                        amax = fmaxf(amax, fmaxf(fabsf(mn.x), fabsf(mn.y)));
-                        m2[i][j] = mn;
+                        if (!FLAT) {
+                            amax = fmaxf(amax, fmaxf(fabsf(mn.x), fabsf(mn.y)));
+                            m2[i][j] = mn;
+                        }
                     }
                     rsum[i] = rs2.x + rs2.y;
                 }
                 wide_release(sh, slot, lane);      // the slot's bytes are in registers now
+                if (FLAT) return;                  // nothing is written in the flat layout
                 // tile absmax: the 8 lanes {c8 ^ 1} x {4 row groups} share a 16x16 tile
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
@@ -410,7 +436,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             };
             if (full_band) band(std::true_type{});
             else band(std::false_type{});
-            if (rsub == 0 && (c8 & 1) == 0) d.m_absmax[tile_id] = A;     // one lane per tile
+            if (!FLAT && rsub == 0 && (c8 & 1) == 0) d.m_absmax[tile_id] = A;     // one lane per tile
             // row sums over this warp's 64 columns: halving butterfly over the 8 column groups (4 shuffles instead
             // of 12); lane c8 ends up with the sum of row rsub + 4 * ((c8 >> 1) & 3) when c8 is even
             {
@@ -583,6 +609,193 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
 }
 
 // ------------------------------------------------------------------------------------------------
+// flat-layout apply pass (CAME8bitFull / CAME8bitMemory, column count a multiple of 256): g, m, p -> m, p.
+// The momentum is recomputed from g and the old codes (the un-quantised value feeds the update, as in
+// kCameFactoredExpAvgResPrepare + kCameFactoredParamUpdate, came_kernels.cu:2246-2305, 2487-2511), re-quantised
+// with one absmax per 256-column row segment, and the parameter is updated in the same pass.
+// Bands of 8 rows x up to 1024 columns; warp w owns the 256-column segment (w & 3) of rows 2*(w >> 2) and
+// 2*(w >> 2) + 1 of the band: a warp = one flat block at a time, its absmax is a warp reduction.
+// ------------------------------------------------------------------------------------------------
+constexpr int FL_BAND = 8;
+constexpr int FL_BANDS = W_TR / FL_BAND;      // 16
+template <typename T> struct FlatCfg {
+    static constexpr int ROW = W_TC * (int)sizeof(T);
+    static constexpr int STAGE = FL_BAND * (2 * ROW + W_MROW);       // g rows, p rows, code rows
+    static constexpr int STAGES = sizeof(T) == 2 ? 4 : 2;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+    constexpr int STAGES = FlatCfg<T>::STAGES, STAGE = FlatCfg<T>::STAGE, ROW = FlatCfg<T>::ROW;
+    extern __shared__ __align__(128) unsigned char smem[];
+    WideShared* sh = reinterpret_cast<WideShared*>(smem + STAGES * STAGE);
+    float* s_rows = reinterpret_cast<float*>(sh + 1);   // [2][2][W_TR]  per item: r_i / clip, R'_i
+    float* s_cols = s_rows + 4 * W_TR;                  // [2][2][W_TC]  per item: c_j, C'_j
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], W_WARPS); }
+        sh->abort = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (warp == W_WARPS) {      // producer: lanes 0-7 copy the band's g rows, 8-15 its code rows, 16-23 its p rows
+        int q = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const WideItem it = wide_item<T>(a, work[item], true);
+            const unsigned char* p_src = reinterpret_cast<const unsigned char*>(a.descs[it.tensor].p) +
+                                         (int64_t)it.row0 * it.a_pitch + (int64_t)it.col0 * sizeof(T);
+            const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(T), m_bytes = (uint32_t)it.wcols;
+            const int nb = min(FL_BANDS, (it.R - it.row0 + FL_BAND - 1) / FL_BAND);
+            for (int band = 0; band < nb; ++band, ++q) {
+                const int slot = q % STAGES;
+                if (q >= STAGES && !wide_wait(&sh->empty[slot], ((q / STAGES) - 1) & 1, sh, a, lane)) return;
+                const int rows = min(FL_BAND, it.R - it.row0 - band * FL_BAND);
+                if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (2 * a_bytes + m_bytes));
+                __syncwarp();
+                const int r = lane & 7, which = lane >> 3;
+                if (r < rows && which < 3) {
+                    const int64_t row = band * FL_BAND + r;
+                    unsigned char* st = smem + slot * STAGE;
+                    if (which == 0) bulk_g2s(st + r * ROW, it.a_src + row * it.a_pitch, a_bytes, &sh->full[slot]);
+                    else if (which == 1) bulk_g2s(st + 2 * FL_BAND * ROW + r * W_MROW, it.m_src + row * it.m_pitch, m_bytes, &sh->full[slot]);
+                    else bulk_g2s(st + FL_BAND * ROW + r * ROW, p_src + row * it.a_pitch, a_bytes, &sh->full[slot]);
+                }
+            }
+        }
+        return;
+    }
+    const int chunk = warp & 3, rpair = warp >> 2;
+    const int cl = chunk * 256 + lane * 8;
+    const u64 magic = splat(ROUND_MAGIC);
+    int q = 0, buf = 0;
+    bool aborted = false;
+
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, buf ^= 1) {
+        const WideItem it = wide_item<T>(a, work[item], true);
+        const CameTensorDesc& d = a.descs[it.tensor];
+        const Scratch& s = a.scr[it.tensor];
+        const CameHyper& h = a.hyp[d.group];
+        const int R = it.R, C = it.C;
+        const bool active = cl < it.wcols;
+        const int col = it.col0 + cl;
+        float* sr = s_rows + buf * 2 * W_TR;       // [0]: r / clip, [1]: R'
+        float* sc = s_cols + buf * 2 * W_TC;       // [0]: c, [1]: C'
+        if (!aborted) {
+            const bool clamp = d.flags & CAME_F_SQ_CLAMP, cr = d.flags & CAME_F_RESROW_CLAMP;
+            float mean = warp_vector_sum(s.rowblk, s.nbR, lane) / (float)R;
+            mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
+            float mean2 = warp_vector_sum(s.rowblk2, s.nbR, lane) / (float)R;
+            mean2 = guard_mean(mean2, d.flags & CAME_F_RESROW_FIX, cr);
+            const float inv_clip = 1.0f / s.scal[1];
+            for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS) {
+                const bool in = it.row0 + i < R;
+                sr[i] = in ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
+                sr[W_TR + i] = in ? row_factor(s.Rr[it.row0 + i], mean2, cr) : 0.0f;
+            }
+            for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS) {
+                sc[i] = col_factor(s.vc[it.col0 + i], clamp);
+                sc[W_TC + i] = col_factor(s.Rc[it.col0 + i], d.flags & CAME_F_RESCOL_CLAMP);
+            }
+        }
+        named_sync(1, W_CONSUMERS);     // met once per item by every consumer warp, also after a failed wait
+        if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) { aborted = true; continue; }
+        u64 cf2[4], cr2[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
+            cr2[j] = active ? pk(sc[W_TC + cl + 2 * j], sc[W_TC + cl + 2 * j + 1]) : F2ZERO;
+        }
+        const int nb = min(FL_BANDS, (R - it.row0 + FL_BAND - 1) / FL_BAND);
+        const int wd_mode = h.weight_decay == 0.0f ? 0 : ((d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 3 : 1));
+        const u64 om2 = splat(h.om_beta1), dmul2 = splat(h.decay_mul), nwdlr2 = splat(-h.wd_lr), nlr2 = splat(-h.lr);
+        const float beta1 = h.beta1;
+        // absmax of this warp's two flat blocks, one band ahead
+        const int64_t blocks_per_row = C >> 8;
+        float* amax_blk = d.m_absmax + (int64_t)(it.row0 + 2 * rpair) * blocks_per_row + (col >> 8);
+        float an[2] = {1.0f, 1.0f};
+        if (active) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+                if (it.row0 + 2 * rpair + t < R) an[t] = amax_blk[(int64_t)t * blocks_per_row];
+        }
+        bool ok = true;
+#pragma unroll 1
+        for (int k = 0; k < nb; ++k, ++q) {
+            const int slot = q % STAGES;
+            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) { ok = false; break; }
+            if (!active) { wide_release(sh, slot, lane); continue; }
+            const unsigned char* st = smem + slot * STAGE;
+            const int brow = it.row0 + k * FL_BAND + 2 * rpair;
+            float a_old[2] = {an[0], an[1]};
+            if (k + 1 < nb) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+                    if (brow + FL_BAND + t < R) an[t] = amax_blk[(int64_t)((k + 1) * FL_BAND + t) * blocks_per_row];
+            }
+            u64 g2[2][4], p2[2][4];
+            uint2 mv[2];
+            float ra[2], rr[2];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int r = 2 * rpair + t;
+                wide_run8(reinterpret_cast<const T*>(st + r * ROW) + cl, g2[t]);
+                wide_run8(reinterpret_cast<const T*>(st + FL_BAND * ROW + r * ROW) + cl, p2[t]);
+                mv[t] = *reinterpret_cast<const uint2*>(st + 2 * FL_BAND * ROW + r * W_MROW + cl);
+                ra[t] = sr[k * FL_BAND + r];
+                rr[t] = sr[W_TR + k * FL_BAND + r];
+            }
+            wide_release(sh, slot, lane);
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                if (brow + t >= R) continue;       // uniform over the warp
+                const uint32_t mx = mv[t].x ^ 0x80808080u, my = mv[t].y ^ 0x80808080u;
+                const u64 ra2 = splat(ra[t]), scb2 = splat((a_old[t] / QMAX_I8) * beta1), rr2 = splat(rr[t]);
+                u64 mn[4];
+                float amax = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const u64 u2 = mul2(mul2(g2[t][j], ra2), cf2[j]);
+                    mn[j] = fma2(om2, u2, mul2(codes_to_f2(j < 2 ? mx : my, (j & 1) * 2), scb2));
+                    amax = fmaxf(amax, fmaxf(fabsf(mn[j].x), fabsf(mn[j].y)));
+                }
+                amax = warp_max(amax);
+                const float A = fix_absmax(amax);
+                const int64_t off = (int64_t)(brow + t) * C + col;
+                uint32_t out[2];
+                if (recip_safe(A)) {      // uniform: A is a warp-wide value
+                    const u64 s127 = splat(QMAX_I8 / A);
+                    u64 y[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) y[j] = fma2(mn[j], s127, magic);
+                    out[0] = pack_codes4(y[0], y[1]);
+                    out[1] = pack_codes4(y[2], y[3]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                        out[e] = ((uint32_t)quant_i8_div(mn[2 * e].x, A) & 0xffu) | (((uint32_t)quant_i8_div(mn[2 * e].y, A) & 0xffu) << 8) |
+                                 (((uint32_t)quant_i8_div(mn[2 * e + 1].x, A) & 0xffu) << 16) | (((uint32_t)quant_i8_div(mn[2 * e + 1].y, A) & 0xffu) << 24);
+                }
+                *reinterpret_cast<uint2*>(reinterpret_cast<int8_t*>(d.m) + off) = make_uint2(out[0], out[1]);
+                if (lane == 0) amax_blk[(int64_t)(k * FL_BAND + t) * blocks_per_row] = A;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const u64 upd = mul2(mul2(mn[j], rr2), cr2[j]);
+                    u64 pv = p2[t][j];
+                    if (wd_mode == 1) pv = fma2(nwdlr2, pv, pv);
+                    else if (wd_mode == 2) pv = round_pair<T>(mul2(pv, dmul2));
+                    else if (wd_mode == 3) pv = round_pair<T>(fma2(nwdlr2, pv, pv));
+                    p2[t][j] = fma2(nlr2, upd, pv);
+                }
+                wide_store8(reinterpret_cast<T*>(d.p) + off, p2[t]);
+            }
+        }
+        if (!ok) { aborted = true; continue; }
+    }
+    if (aborted && warp == 0) wide_drain(sh, STAGES);
+}
+
+// ------------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------------
 template <typename T> static constexpr size_t moment_smem() {
@@ -591,6 +804,10 @@ template <typename T> static constexpr size_t moment_smem() {
 }
 template <typename T> static constexpr size_t apply_smem() {
     return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + sizeof(WideShared) + 2 * (W_TR + W_TC) * sizeof(float);
+}
+
+template <typename T> static constexpr size_t flat_smem() {
+    return (size_t)FlatCfg<T>::STAGES * FlatCfg<T>::STAGE + sizeof(WideShared) + 4 * (W_TR + W_TC) * sizeof(float);
 }
 
 template <typename K>
@@ -612,10 +829,24 @@ cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& 
                               cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
     if (kernel == KID_MOMENT) {
+        if (key.mode == CAME_MODE_FLAT8) {
+            switch (key.g_dtype) {
+                case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, true>, moment_smem<float>(), a, work, n, st);
+                case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, true>, moment_smem<__half>(), a, work, n, st);
+                default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, true>, moment_smem<__nv_bfloat16>(), a, work, n, st);
+            }
+        }
         switch (key.g_dtype) {
-            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float>, moment_smem<float>(), a, work, n, st);
-            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half>, moment_smem<__half>(), a, work, n, st);
-            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16>, moment_smem<__nv_bfloat16>(), a, work, n, st);
+            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, false>, moment_smem<float>(), a, work, n, st);
+            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, false>, moment_smem<__half>(), a, work, n, st);
+            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, false>, moment_smem<__nv_bfloat16>(), a, work, n, st);
+        }
+    }
+    if (kernel == KID_APPLY_FLAT) {
+        switch (key.g_dtype) {
+            case CAME_DT_F32: return launch_persistent(k_apply_flat8_wide<float>, flat_smem<float>(), a, work, n, st);
+            case CAME_DT_F16: return launch_persistent(k_apply_flat8_wide<__half>, flat_smem<__half>(), a, work, n, st);
+            default: return launch_persistent(k_apply_flat8_wide<__nv_bfloat16>, flat_smem<__nv_bfloat16>(), a, work, n, st);
         }
     }
     if (kernel == KID_APPLY) {

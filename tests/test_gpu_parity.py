@@ -23,7 +23,7 @@ H_NOWD = dict(H_DEFAULT, weight_decay=0.0)
 
 EDGE_SHAPES = [(1, 40), (40, 1), (15, 17), (16, 16), (17, 255), (255, 257), (256, 256), (257, 16), (1,), (255,),
                (256,), (257,), (700,)]
-ALIGNED_SHAPES = [(256, 512), (128, 1024), (384, 272), (64, 48), (300, 256), (17, 768), (4096,), (300,)]
+ALIGNED_SHAPES = [(256, 512), (128, 1024), (384, 272), (64, 48), (300, 256), (17, 768), (135, 1280), (4096,), (300,)]
 
 
 def _dt(name):
