@@ -120,14 +120,21 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.rowblk = take((size_t)g.nbR); s.rowblk2 = take((size_t)g.nbR);
         s.scal = take(4);
         s.rowpart = take((size_t)std::max(g.tiles_c, g.ptiles_c) * (size_t)g.R);
-        s.colpart = take((size_t)std::max(g.tiles_r, g.ptiles_r) * (size_t)g.C);
+        s.sq_col_parts = g.tiles_r;
+        int fa_groups = 1, fa_ng = 1, fa_rb = 1, fa_stages = 3;
+        if (vec_flags(d).k == 2) {
+            fused_sq_geometry(g.C, elem_bytes(d.g_dtype), &fa_groups, &fa_ng, &fa_rb, &fa_stages);
+            s.sq_col_parts = g.tiles_r * fa_groups;
+        }
+        s.colpart = take((size_t)std::max(s.sq_col_parts, g.ptiles_r) * (size_t)g.C);
         s.spart = take(std::max((size_t)g.tiles_r * (size_t)g.tiles_c, (size_t)g.nbC));
         s.fac = (d.mode == CAME_MODE_FLAT8 && vec_flags(d).flat != 2) ? take(2 * (size_t)(g.R + g.C)) : nullptr;
         if (vec_flags(d).p2 == 2) s.res_eps_deferred = 1;
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
-            s.fa_rb = fused_sq_rows_per_batch(g.C * elem_bytes(d.g_dtype), g.C);
-            s.tpart = take((size_t)g.tiles_r * (size_t)g.C);
+            s.fa_rb = fa_rb;
+            s.fa_stages = fa_stages;
+            s.tpart = take((size_t)s.sq_col_parts * (size_t)g.C);
         }
     }
     if (out) *out = s;
@@ -321,14 +328,19 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
     auto fusedA = [&](int i) { return D[i].cols != 0 && vf[i].k == 2; };
     auto twopass = [&](int i) { return D[i].cols != 0 && vf[i].k != 2; };
-    auto groups_per_thread = [&](int i) { return (int)cdiv(cdiv(D[i].cols, 8), 512); };
-    build(KID_SQ_PARTIALS, fusedA, [&](int i) { return Key{D[i].g_dtype, 0, groups_per_thread(i), 2}; },
+    auto fused_code = [&](int i) {      // column groups per thread | warp groups << 4
+        int groups, ng, rb, stages;
+        fused_sq_geometry(D[i].cols, elem_bytes(D[i].g_dtype), &groups, &ng, &rb, &stages);
+        return ng | (groups << 4);
+    };
+    build(KID_SQ_PARTIALS, fusedA, [&](int i) { return Key{D[i].g_dtype, 0, fused_code(i), 2}; },
           [&](int i) { return (int64_t)geo[i].tiles_r; });
-    for (auto& it : plan->launches)   // slot size of each fused launch = the largest among its tensors
+    for (auto& it : plan->launches)   // shared memory of each fused launch = the largest ring among its tensors
         if (it.kernel == KID_SQ_PARTIALS)
             for (int i = 0; i < n_tensors; ++i)
-                if (fusedA(i) && D[i].g_dtype == it.key.g_dtype && groups_per_thread(i) == it.key.mode)
-                    it.extra = std::max(it.extra, (size_t)scr[i].fa_rb * (size_t)D[i].cols * elem_bytes(D[i].g_dtype));
+                if (fusedA(i) && D[i].g_dtype == it.key.g_dtype && fused_code(i) == it.key.mode)
+                    it.extra = std::max(it.extra, (size_t)scr[i].fa_stages * (size_t)scr[i].fa_rb * (size_t)D[i].cols *
+                                                      elem_bytes(D[i].g_dtype));
     build(KID_SQ_PARTIALS, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });

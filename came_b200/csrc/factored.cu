@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
                 if (RES && s.res_eps_deferred) acc += (float)C * h.eps1;
                 acc = acc / (float)C;
             } else {
-                const int parts = RES ? s.ptiles_r : s.tiles_r;
+                const int parts = RES ? s.ptiles_r : s.sq_col_parts;
                 for (int t = 0; t < parts; ++t) acc += s.colpart[(int64_t)t * C + idx];
                 if (fused) {
                     acc += (float)R * h.eps0;

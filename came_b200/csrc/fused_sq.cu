@@ -22,7 +22,6 @@ namespace came {
 
 constexpr int FA_THREADS = 512;
 constexpr int FA_WARPS = FA_THREADS / 32;
-constexpr int FA_STAGES = 3;
 constexpr int FA_RB_MAX = 16;
 
 // 8 consecutive staged elements -> 4 packed fp32 pairs
@@ -68,10 +67,13 @@ __device__ __forceinline__ float warp_reduce_rows(float* v, int lane) {
     return t;
 }
 
-// Shared bookkeeping of one CTA: ring barriers and the abort flag every waiter polls (same protocol as the momentum / apply passes).
+constexpr int FA_MAX_STAGES = 8;
+
+// Shared bookkeeping of one CTA: ring barriers and the abort flag every waiter polls (same protocol as the
+// momentum / apply passes).
 struct FaShared {
-    uint64_t full[FA_STAGES];
-    uint64_t empty[FA_STAGES];
+    uint64_t full[FA_MAX_STAGES];
+    uint64_t empty[FA_MAX_STAGES];
     int abort;
     int pad;
 };
@@ -88,24 +90,30 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, FaShared
 
 // Warps 0..15 compute; warp 16 only issues the bulk copies (a bulk-copy instruction blocks while the copy
 // engine's queue is full, which would otherwise stall a computing warp for about as long as a batch takes).
-template <typename TG, int NG>
+//
+// GROUPS = 2 (matrices of at most 2048 columns): the computing warps form two groups of 8 that take alternate
+// batches, each with its own barrier, so that one group sweeps while the other sits in the latency of its
+// row-sum exchange; each group spans a whole row with 256 threads, which also keeps every thread busy down to
+// 2048 columns.  NG = column groups (of 8 columns) per thread within its group.
+// KEEP (NG <= 2): batches are small enough for the squares to stay in registers between the two sweeps.
+template <typename TG, int NG, int GROUPS>
 __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work) {
-    // most rows a batch can hold for this column count.  One column group per thread (cols <= 4096): batches are
-    // capped at 4 rows and the squares stay in registers between the two sweeps instead of being re-read.
-    constexpr bool KEEP = NG == 1;
-    constexpr int RBM = NG == 1 ? 4 : (NG == 2 ? 8 : 4);
+    constexpr bool KEEP = NG <= 2;
+    constexpr int RBM = KEEP ? 4 / NG : 4;                 // most rows of a batch (the plan sizes batches accordingly)
+    constexpr int GT = FA_THREADS / GROUPS;                // threads of a group
+    constexpr int WPG = FA_WARPS / GROUPS;                 // warps of a group
     extern __shared__ __align__(128) unsigned char smem[];
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
     const Scratch& s = a.scr[w.tensor];
     const CameHyper& h = a.hyp[d.group];
     const int R = (int)d.rows, C = (int)d.cols;
-    const int rb = s.fa_rb;
+    const int rb = s.fa_rb, nstages = s.fa_stages;
     const int row_bytes = C * (int)sizeof(TG);
     const int stage_bytes = rb * row_bytes;
-    FaShared* sh = reinterpret_cast<FaShared*>(smem + FA_STAGES * stage_bytes);
-    float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS][FA_RB_MAX], double-buffered by batch
-    float* s_old = s_part + 2 * FA_WARPS * FA_RB_MAX;                // [K_TR] dequantised old v_row of the strip's rows
+    FaShared* sh = reinterpret_cast<FaShared*>(smem + nstages * stage_bytes);
+    float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS][4], double-buffered by batch
+    float* s_old = s_part + 2 * FA_WARPS * 4;                        // [K_TR] dequantised old v_row of the strip's rows
 
     const int strip = w.tile;
     const int row0 = strip * K_TR;
@@ -115,7 +123,7 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     const unsigned char* g_src = reinterpret_cast<const unsigned char*>(d.g);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < FA_STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], FA_WARPS); }
+        for (int i = 0; i < nstages; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], WPG); }
         sh->abort = 0;
         mbar_init_fence();
     }
@@ -130,9 +138,11 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     __syncthreads();
 
     if (warp == FA_WARPS) {      // producer: lane r copies row r of batch b
-        for (int b = 0; b < nbatch; ++b) {
-            const int slot = b % FA_STAGES;
-            if (b >= FA_STAGES && !fa_wait(&sh->empty[slot], ((b / FA_STAGES) - 1) & 1, sh, a, lane)) return;
+        int slot = 0;
+        uint32_t phase = 1;      // parity of the slot's previous use (meaningless during the first lap)
+        for (int b = 0; b < nbatch; ++b, ++slot) {
+            if (slot == nstages) { slot = 0; phase ^= 1u; }
+            if (b >= nstages && !fa_wait(&sh->empty[slot], phase, sh, a, lane)) return;
             const int rows = min(rb, nrows - b * rb);
             if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (uint32_t)row_bytes);
             __syncwarp();
@@ -143,47 +153,42 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
         return;
     }
 
-    // this thread's column groups: 8 consecutive columns starting at 8 * (threadIdx.x + FA_THREADS * j)
+    const int group = threadIdx.x / GT, tig = threadIdx.x - group * GT, wig = warp - group * WPG;
+    // this thread's column groups: 8 consecutive columns starting at 8 * (tig + GT * j)
     bool gvalid[NG];
     u64 colb[NG][4], colT[NG][4];
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
-        gvalid[j] = (threadIdx.x + FA_THREADS * j) * 8 < C;
+        gvalid[j] = (tig + GT * j) * 8 < C;
 #pragma unroll
         for (int e = 0; e < 4; ++e) { colb[j][e] = F2ZERO; colT[j][e] = F2ZERO; }
     }
     bool ok = true;
-#ifdef CAME_WIDE_PROFILE
-    long long pf_wait = 0, pf_s1 = 0, pf_bar = 0, pf_fin = 0, pf_s2 = 0;
-    const long long pf_start = clock64();
-#endif
+    int nb_done = 0;       // batches this group has gone through (selects the s_part buffer)
 
-    for (int b = 0; b < nbatch; ++b) {
-        const int slot = b % FA_STAGES;
-        // After a failed wait a warp keeps walking the batches without touching data, so that it still meets
-        // the other consumer warps at the hardware barrier below once per batch (nobody is left waiting).
-#ifdef CAME_WIDE_PROFILE
-        const long long c0 = clock64();
-#endif
-        if (ok && !fa_wait(&sh->full[slot], (b / FA_STAGES) & 1, sh, a, lane)) ok = false;
-#ifdef CAME_WIDE_PROFILE
-        const long long c1 = clock64();
-#endif
-        if (!ok) { named_sync(1, FA_THREADS); continue; }
+    int slot = group;      // ring position of batch b, advanced without a division (GROUPS <= slots)
+    uint32_t phase = 0;
+    for (int b = group; b < nbatch; b += GROUPS, ++nb_done, slot += GROUPS) {
+        if (slot >= nstages) { slot -= nstages; phase ^= 1u; }
+        // After a failed wait a warp keeps walking its batches without touching data, so that it still meets
+        // the other warps of its group at the hardware barrier below once per batch (nobody is left waiting).
+        if (ok && !fa_wait(&sh->full[slot], phase, sh, a, lane)) ok = false;
+        if (!ok) { named_sync(1 + group, GT); continue; }
         const int rows = min(rb, nrows - b * rb);
         const unsigned char* st = smem + slot * stage_bytes;
-        float* part = s_part + (b & 1) * (FA_WARPS * FA_RB_MAX);
+        float* part = s_part + (nb_done & 1) * (FA_WARPS * 4) + group * (WPG * 4);
 
         // sweep 1: row sums and column sums of g^2.  Row partials stay in registers (static indices: the loops
         // are fully unrolled and guarded) and are reduced across the warp together.
-        float rp[RBM];
-        u64 sqk[KEEP ? RBM : 1][4];      // KEEP: g^2 of this thread's elements, reused by sweep 2
+        float rp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        u64 sqk[KEEP ? RBM : 1][KEEP ? NG : 1][4];      // KEEP: g^2 of this thread's elements, reused by sweep 2
 #pragma unroll
         for (int r = 0; r < RBM; ++r) {
-            rp[r] = 0.0f;
             if (KEEP) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) sqk[KEEP ? r : 0][e] = F2ZERO;
+                for (int j = 0; j < NG; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sqk[KEEP ? r : 0][KEEP ? j : 0][e] = F2ZERO;
             }
             if (r < rows) {
                 u64 racc = F2ZERO;
@@ -191,12 +196,12 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
                 for (int j = 0; j < NG; ++j) {
                     if (gvalid[j]) {
                         u64 g2[4];
-                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
+                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (tig + GT * j) * 8, g2);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             if (KEEP) {
                                 const u64 sq = mul2(g2[e], g2[e]);
-                                sqk[KEEP ? r : 0][e] = sq;
+                                sqk[KEEP ? r : 0][KEEP ? j : 0][e] = sq;
                                 colb[j][e] = add2(colb[j][e], sq);
                                 racc = add2(racc, sq);
                             } else {
@@ -213,67 +218,41 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->empty[slot]);
         }
-        if (RBM > 8 && rows > 8) {
-            float v16[16];
-#pragma unroll
-            for (int r = 0; r < 16; ++r) v16[r] = r < RBM ? rp[r] : 0.0f;
-            const float t = warp_reduce_rows<16>(v16, lane);
-            if ((lane & 1) == 0) part[warp * FA_RB_MAX + ((lane >> 1) & 15)] = t;
-        } else if (RBM > 4 && rows > 4) {
-            float v8[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) v8[r] = r < RBM ? rp[r] : 0.0f;
-            const float t = warp_reduce_rows<8>(v8, lane);
-            if ((lane & 3) == 0) part[warp * FA_RB_MAX + ((lane >> 2) & 7)] = t;
-        } else {
-            float v4[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) v4[r] = rp[r];
-            const float t = warp_reduce_rows<4>(v4, lane);
-            if ((lane & 7) == 0) part[warp * FA_RB_MAX + ((lane >> 3) & 3)] = t;
+        {
+            const float t = warp_reduce_rows<4>(rp, lane);
+            if ((lane & 7) == 0) part[wig * 4 + ((lane >> 3) & 3)] = t;
         }
-        // barrier among the 16 consumer warps: the per-warp row partials of this batch are complete
-#ifdef CAME_WIDE_PROFILE
-        const long long c2 = clock64();
-#endif
-        named_sync(1, FA_THREADS);
-#ifdef CAME_WIDE_PROFILE
-        const long long c3 = clock64();
-#endif
+        // barrier among the warps of this group: the per-warp row partials of the batch are complete
+        named_sync(1 + group, GT);
 
-        // every warp finishes the row sums itself (lane r: row r), so no second barrier is needed; warp 0
-        // publishes v_row.  Mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the dequantised state.
+        // every warp finishes the row sums itself (lane r: row r), so no second barrier is needed; the group's first
+        // warp publishes v_row.  Mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the old state.
         float wrow = 0.0f;
         if (lane < rows) {
             float sum = 0.0f;
 #pragma unroll
-            for (int ww = 0; ww < FA_WARPS; ++ww) sum += part[ww * FA_RB_MAX + lane];
+            for (int ww = 0; ww < WPG; ++ww) sum += part[ww * 4 + lane];
             const int row = row0 + b * rb + lane;
             const float mean = (sum + (float)C * h.eps0) / (float)C;
             const float v = s_old[b * rb + lane] * h.beta2 + h.om_beta2 * mean;
-            if (warp == 0) s.vr[row] = v;
+            if (wig == 0) s.vr[row] = v;
             wrow = v > 0.0f ? 1.0f / v : 0.0f;
         }
-#ifdef CAME_WIDE_PROFILE
-        const long long c4 = clock64();
-#endif
         // sweep 2: column sums of g^2 / v_row
 #pragma unroll
         for (int r = 0; r < RBM; ++r) {
             if (r < rows) {
                 const u64 w2 = splat(__shfl_sync(0xffffffffu, wrow, r));
-                if (KEEP) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) colT[0][e] = fma2(sqk[KEEP ? r : 0][e], w2, colT[0][e]);
-                } else {
+                for (int j = 0; j < NG; ++j) {
+                    if (KEEP) {
 #pragma unroll
-                    for (int j = 0; j < NG; ++j) {
-                        if (gvalid[j]) {
-                            u64 g2[4];
-                            smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (threadIdx.x + FA_THREADS * j) * 8, g2);
+                        for (int e = 0; e < 4; ++e) colT[j][e] = fma2(sqk[KEEP ? r : 0][KEEP ? j : 0][e], w2, colT[j][e]);
+                    } else if (gvalid[j]) {
+                        u64 g2[4];
+                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (tig + GT * j) * 8, g2);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) colT[j][e] = fma2(mul2(g2[e], g2[e]), w2, colT[j][e]);
-                        }
+                        for (int e = 0; e < 4; ++e) colT[j][e] = fma2(mul2(g2[e], g2[e]), w2, colT[j][e]);
                     }
                 }
             }
@@ -282,21 +261,13 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->empty[slot]);
         }
-#ifdef CAME_WIDE_PROFILE
-        const long long c5 = clock64();
-        pf_wait += c1 - c0; pf_s1 += c2 - c1; pf_bar += c3 - c2; pf_fin += c4 - c3; pf_s2 += c5 - c4;
-#endif
     }
-#ifdef CAME_WIDE_PROFILE
-    if ((blockIdx.x == 0 || blockIdx.x == 200) && lane == 0 && (warp == 0 || warp == 9))
-        printf("sqstat NG %d cta %d warp %d rb %d: total %lld wait %lld sweep1 %lld barrier %lld finalize %lld sweep2 %lld batches %d\n", NG,
-               blockIdx.x, warp, rb, clock64() - pf_start, pf_wait, pf_s1, pf_bar, pf_fin, pf_s2, nbatch);
-#endif
     if (!ok) return;      // the status word is set; the partial sums of this strip stay unwritten
+    // one set of column partials per (strip, group)
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
         if (gvalid[j]) {
-            const int64_t off = (int64_t)strip * C + (threadIdx.x + FA_THREADS * j) * 8;
+            const int64_t off = (int64_t)(strip * GROUPS + group) * C + (tig + GT * j) * 8;
             reinterpret_cast<float4*>(s.colpart + off)[0] = make_float4(colb[j][0].x, colb[j][0].y, colb[j][1].x, colb[j][1].y);
             reinterpret_cast<float4*>(s.colpart + off)[1] = make_float4(colb[j][2].x, colb[j][2].y, colb[j][3].x, colb[j][3].y);
             reinterpret_cast<float4*>(s.tpart + off)[0] = make_float4(colT[j][0].x, colT[j][0].y, colT[j][1].x, colT[j][1].y);
@@ -305,48 +276,61 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     }
 }
 
-// rows per staged batch for a row of `row_bytes`: as many as fit 64 KB per slot; at most 4 when a thread owns a
-// single column group (cols <= 4096), else at most 8
-int fused_sq_rows_per_batch(int64_t row_bytes, int64_t cols) {
-    int64_t rb = (64 * 1024) / row_bytes;
-    const int64_t cap = cols <= (int64_t)FA_THREADS * 8 ? 4 : 8;
-    if (rb > cap) rb = cap;
-    if (rb < 1) rb = 1;
-    return (int)rb;
+// Geometry of the fused first pass for a matrix of `cols` columns of `elem_bytes` each:
+//   groups   2 up to 2048 columns (two 8-warp groups on alternate batches), else 1
+//   ng       column groups of 8 per thread within its group (1..4)
+//   rb       rows per staged batch: at most 4/ng while the squares are kept in registers (ng <= 2), at most 4
+//            otherwise, and never more than fit 64 KB
+//   stages   ring slots: as many as fit ~160 KB, between 3 and 8
+void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb, int* stages) {
+    const int g = cols <= (int64_t)FA_THREADS * 4 ? 2 : 1;
+    const int gt = FA_THREADS / g;
+    const int n = (int)((cols / 8 + gt - 1) / gt);
+    const int64_t row_bytes = cols * elem_bytes;
+    int64_t r = (64 * 1024) / row_bytes;
+    const int64_t cap = n <= 2 ? 4 / n : 4;
+    if (r > cap) r = cap;
+    if (r < 1) r = 1;
+    int64_t st = (160 * 1024) / (r * row_bytes);
+    if (st > FA_MAX_STAGES) st = FA_MAX_STAGES;
+    if (st < 3) st = 3;
+    *groups = g; *ng = n < 1 ? 1 : n; *rb = (int)r; *stages = (int)st;
 }
 
 bool fused_sq_eligible(int64_t cols, int elem_bytes) {
     return cols % 8 == 0 && cols <= (int64_t)FA_THREADS * 8 * 4 && cols * elem_bytes <= 64 * 1024;
 }
 
-template <typename TG, int NG>
+template <typename TG, int NG, int GROUPS>
 static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, size_t smem, cudaStream_t st) {
-    cudaError_t e = cudaFuncSetAttribute(k_sqstat_fused<TG, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k_sqstat_fused<TG, NG, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    k_sqstat_fused<TG, NG><<<n, FA_THREADS + 32, smem, st>>>(a, work);
+    k_sqstat_fused<TG, NG, GROUPS><<<n, FA_THREADS + 32, smem, st>>>(a, work);
     return cudaGetLastError();
 }
 
 template <typename TG>
-static cudaError_t launch_ng(int ng, const StepArgs& a, const Work* work, int n, size_t smem, cudaStream_t st) {
+static cudaError_t launch_ng(int ng, int groups, const StepArgs& a, const Work* work, int n, size_t smem, cudaStream_t st) {
+    if (groups == 2) return launch_one<TG, 1, 2>(a, work, n, smem, st);      // at most 2048 columns: one column group per thread
     switch (ng) {
-        case 1: return launch_one<TG, 1>(a, work, n, smem, st);
-        case 2: return launch_one<TG, 2>(a, work, n, smem, st);
-        case 3: return launch_one<TG, 3>(a, work, n, smem, st);
-        default: return launch_one<TG, 4>(a, work, n, smem, st);
+        case 1: return launch_one<TG, 1, 1>(a, work, n, smem, st);
+        case 2: return launch_one<TG, 2, 1>(a, work, n, smem, st);
+        case 3: return launch_one<TG, 3, 1>(a, work, n, smem, st);
+        default: return launch_one<TG, 4, 1>(a, work, n, smem, st);
     }
 }
 
-// key.mode carries the number of column groups per thread (1..4); all tensors of one launch share it and
-// `max_stage_bytes` is the largest slot (rows per batch x row bytes) among them
-cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_stage_bytes,
+// key.mode carries ng | (groups << 4); all tensors of one launch share it and `max_ring_bytes` is the largest
+// ring (slots x rows per batch x row bytes) among them
+cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_ring_bytes,
                             cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
-    const size_t smem = FA_STAGES * max_stage_bytes + sizeof(FaShared) + (2 * FA_WARPS * FA_RB_MAX + K_TR) * sizeof(float);
+    const size_t smem = max_ring_bytes + sizeof(FaShared) + (2 * FA_WARPS * 4 + K_TR) * sizeof(float);
+    const int ng = key.mode & 15, groups = key.mode >> 4;
     switch (key.g_dtype) {
-        case CAME_DT_F32: return launch_ng<float>(key.mode, a, work, n, smem, st);
-        case CAME_DT_F16: return launch_ng<__half>(key.mode, a, work, n, smem, st);
-        default: return launch_ng<__nv_bfloat16>(key.mode, a, work, n, smem, st);
+        case CAME_DT_F32: return launch_ng<float>(ng, groups, a, work, n, smem, st);
+        case CAME_DT_F16: return launch_ng<__half>(ng, groups, a, work, n, smem, st);
+        default: return launch_ng<__nv_bfloat16>(ng, groups, a, work, n, smem, st);
     }
 }
 
