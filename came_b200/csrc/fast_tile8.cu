@@ -327,6 +327,10 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         }
         const u64 om2 = splat(h.om_beta1);
         const float beta1 = h.beta1;
+        // table entries the band loop uses, read once per item (the barriers in the loop make the compiler reload them)
+        int8_t* const m_base = reinterpret_cast<int8_t*>(d.m);
+        float* const m_absmax = d.m_absmax;
+        float* const colpart = s.colpart;
         bool ok = true;
 
 #pragma unroll 1
@@ -402,7 +406,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
                 A = fix_absmax(amax);
-                int8_t* mdst = reinterpret_cast<int8_t*>(d.m) + (int64_t)(brow + rsub) * C + col;
+                int8_t* mdst = m_base + (int64_t)(brow + rsub) * C + col;
                 // the reciprocal form needs a normal 1/A: decided per warp so that the branch never diverges
                 if (__all_sync(0xffffffffu, recip_safe(A))) {
                     // code = rint((m / A) * 127) computed as rint(m * (127 / A)) in one FMA with the rounding constant:
@@ -436,7 +440,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             };
             if (full_band) band(std::true_type{});
             else band(std::false_type{});
-            if (!FLAT && rsub == 0 && (c8 & 1) == 0) d.m_absmax[tile_id] = A;     // one lane per tile
+            if (!FLAT && rsub == 0 && (c8 & 1) == 0) m_absmax[tile_id] = A;     // one lane per tile
             // row sums over this warp's 64 columns: halving butterfly over the 8 column groups (4 shuffles instead
             // of 12); lane c8 ends up with the sum of row rsub + 4 * ((c8 >> 1) & 3) when c8 is even
             {
@@ -458,7 +462,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 upk(colacc[j], lo, hi);
                 lo += __shfl_xor_sync(0xffffffffu, lo, 8);  hi += __shfl_xor_sync(0xffffffffu, hi, 8);
                 lo += __shfl_xor_sync(0xffffffffu, lo, 16); hi += __shfl_xor_sync(0xffffffffu, hi, 16);
-                if (rsub == 0) *reinterpret_cast<float2*>(s.colpart + (int64_t)it.tr * C + col + 2 * j) = make_float2(lo, hi);
+                if (rsub == 0) *reinterpret_cast<float2*>(colpart + (int64_t)it.tr * C + col + 2 * j) = make_float2(lo, hi);
             }
         }
         prev_valid = 1; prev_row0 = it.row0; prev_R = R; prev_tc = it.tc; prev_nw = (it.wcols + 63) >> 6;
@@ -544,6 +548,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
         float a_next = active ? amax_col[0] : 0.0f;     // tile absmax, fetched one band ahead
         const int wd_mode = h.weight_decay == 0.0f ? 0 : ((d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 3 : 1));
         const u64 dmul2 = splat(h.decay_mul), nwdlr2 = splat(-h.wd_lr), nlr2 = splat(-h.lr);
+        TP* const p_base = reinterpret_cast<TP*>(d.p);      // read once per item, not once per band
         bool ok = true;
 
 #pragma unroll 1
@@ -575,7 +580,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
                     rfac[i] = sr[k * W_BAND + r];
                 }
                 wide_release(sh, slot, lane);
-                TP* pdst = reinterpret_cast<TP*>(d.p) + (int64_t)(brow + rsub) * C + col;
+                TP* pdst = p_base + (int64_t)(brow + rsub) * C + col;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t mx = mv[i].x ^ 0x80808080u, my = mv[i].y ^ 0x80808080u;
@@ -713,6 +718,8 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
         // absmax of this warp's two flat blocks, one band ahead
         const int64_t blocks_per_row = C >> 8;
         float* amax_blk = d.m_absmax + (int64_t)(it.row0 + 2 * rpair) * blocks_per_row + (col >> 8);
+        int8_t* const m_base = reinterpret_cast<int8_t*>(d.m);      // read once per item, not once per band
+        T* const p_base = reinterpret_cast<T*>(d.p);
         float an[2] = {1.0f, 1.0f};
         if (active) {
 #pragma unroll
@@ -776,7 +783,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
                         out[e] = ((uint32_t)quant_i8_div(mn[2 * e].x, A) & 0xffu) | (((uint32_t)quant_i8_div(mn[2 * e].y, A) & 0xffu) << 8) |
                                  (((uint32_t)quant_i8_div(mn[2 * e + 1].x, A) & 0xffu) << 16) | (((uint32_t)quant_i8_div(mn[2 * e + 1].y, A) & 0xffu) << 24);
                 }
-                *reinterpret_cast<uint2*>(reinterpret_cast<int8_t*>(d.m) + off) = make_uint2(out[0], out[1]);
+                *reinterpret_cast<uint2*>(m_base + off) = make_uint2(out[0], out[1]);
                 if (lane == 0) amax_blk[(int64_t)(k * FL_BAND + t) * blocks_per_row] = A;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -787,7 +794,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
                     else if (wd_mode == 3) pv = round_pair<T>(fma2(nwdlr2, pv, pv));
                     p2[t][j] = fma2(nlr2, upd, pv);
                 }
-                wide_store8(reinterpret_cast<T*>(d.p) + off, p2[t]);
+                wide_store8(p_base + off, p2[t]);
             }
         }
         if (!ok) { aborted = true; continue; }

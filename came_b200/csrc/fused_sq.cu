@@ -7,7 +7,7 @@
 // which holds because r_i^2 = mean(v_row) / v_row_i and c_j^2 = 1 / v_col_j when no 1e-30 clamp is active
 // (tensors carrying CAME_F_SQ_CLAMP take the two-pass kernels instead).  v_row_i needs the complete row,
 // so a CTA owns whole rows: a strip of 128 rows, staged through shared memory in batches of `rb` rows by
-// bulk asynchronous copies (three slots: two batches in flight while one is computed on), swept twice from
+// bulk asynchronous copies into a ring of three to eight slots, swept twice from
 // shared memory.
 //
 // Replaces kUpdateSqRowQuantized, the column walk of kUpdateSqColQuantizedFinalize and kSumUpdateSq
@@ -17,12 +17,14 @@
 #include "pipeline.cuh"
 
 #include <cstdio>
+#include <algorithm>
+#include <cstdlib>
 
 namespace came {
 
 constexpr int FA_THREADS = 512;
 constexpr int FA_WARPS = FA_THREADS / 32;
-constexpr int FA_RB_MAX = 16;
+constexpr int FA_RB = 16;          // most rows of a staged batch (one per computing warp)
 
 // 8 consecutive staged elements -> 4 packed fp32 pairs
 __device__ __forceinline__ void smem_run8(const __nv_bfloat16* p, u64* out) {
@@ -43,28 +45,6 @@ __device__ __forceinline__ void smem_run8(const __half* p, u64* out) {
 __device__ __forceinline__ void smem_run8(const float* p, u64* out) {
     const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
     out[0] = pk(a.x, a.y); out[1] = pk(a.z, a.w); out[2] = pk(b.x, b.y); out[3] = pk(b.z, b.w);
-}
-
-// Sum N per-lane values v[0..N) over the 32 lanes of a warp with a halving butterfly: after log2(N) exchange
-// steps every lane holds one row's partial, the remaining steps finish it.  Lane L ends with the total of row
-// (L >> (5 - log2 N)) & (N - 1)   (N = 16: (L >> 1) & 15, N = 8: (L >> 2) & 7, N = 4: (L >> 3) & 3).
-template <int N>
-__device__ __forceinline__ float warp_reduce_rows(float* v, int lane) {
-    int mask = 16;
-#pragma unroll
-    for (int n = N; n > 1; n >>= 1, mask >>= 1) {
-        const bool upper = (lane & mask) != 0;
-#pragma unroll
-        for (int i = 0; i < n / 2; ++i) {
-            const float send = upper ? v[i] : v[i + n / 2];
-            const float keep = upper ? v[i + n / 2] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
-        }
-    }
-    float t = v[0];
-#pragma unroll
-    for (; mask > 0; mask >>= 1) t += __shfl_xor_sync(0xffffffffu, t, mask);
-    return t;
 }
 
 constexpr int FA_MAX_STAGES = 8;
@@ -91,17 +71,19 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, FaShared
 // Warps 0..15 compute; warp 16 only issues the bulk copies (a bulk-copy instruction blocks while the copy
 // engine's queue is full, which would otherwise stall a computing warp for about as long as a batch takes).
 //
-// GROUPS = 2 (matrices of at most 2048 columns): the computing warps form two groups of 8 that take alternate
-// batches, each with its own barrier, so that one group sweeps while the other sits in the latency of its
-// row-sum exchange; each group spans a whole row with 256 threads, which also keeps every thread busy down to
-// 2048 columns.  NG = column groups (of 8 columns) per thread within its group.
-// KEEP (NG <= 2): batches are small enough for the squares to stay in registers between the two sweeps.
-template <typename TG, int NG, int GROUPS>
+// A batch of rb rows (a power of two, at most 16) is swept twice from shared memory with two different
+// thread mappings:
+//   row sweep     the 16 warps split the batch into 16 row pieces (16 / rb pieces per row); a warp sums the
+//                 squares of its piece, so a row sum costs one warp reduction and 16 / rb partials in shared
+//                 memory -- no cross-warp tree, and the row's new v_row is completed once per warp;
+//   column sweep  a thread owns the same 8 consecutive columns (NG such groups) for every row and accumulates
+//                 g^2 and g^2 / v_row down the columns.  RS = 2 (matrices of at most 2048 columns): the
+//                 threads form two sets that take the even and the odd rows of a batch, which keeps every
+//                 thread busy; each set leaves its own column partials.
+// Software pipeline: the row sweep of batch i+1 is issued before the column sweep of batch i, with one hardware
+// barrier per batch, so the exchange of row partials never stalls the warps.  A warp holds two ring slots.
+template <typename TG, int NG, int RS>
 __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work) {
-    constexpr bool KEEP = NG <= 2;
-    constexpr int RBM = KEEP ? 4 / NG : 4;                 // most rows of a batch (the plan sizes batches accordingly)
-    constexpr int GT = FA_THREADS / GROUPS;                // threads of a group
-    constexpr int WPG = FA_WARPS / GROUPS;                 // warps of a group
     extern __shared__ __align__(128) unsigned char smem[];
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
@@ -109,11 +91,17 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     const CameHyper& h = a.hyp[d.group];
     const int R = (int)d.rows, C = (int)d.cols;
     const int rb = s.fa_rb, nstages = s.fa_stages;
+    // everything the batch loop needs from the tables in global memory, read once: the barriers in the loop are
+    // memory fences for the compiler, which would otherwise reload these on every batch
+    const float eps0C = (float)C * h.eps0, fC = (float)C, beta2 = h.beta2, om_beta2 = h.om_beta2;
+    float* const vr = s.vr;
+    float* const colpart = s.colpart;
+    float* const tpart = s.tpart;
     const int row_bytes = C * (int)sizeof(TG);
     const int stage_bytes = rb * row_bytes;
     FaShared* sh = reinterpret_cast<FaShared*>(smem + nstages * stage_bytes);
-    float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS][4], double-buffered by batch
-    float* s_old = s_part + 2 * FA_WARPS * 4;                        // [K_TR] dequantised old v_row of the strip's rows
+    float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS] row-piece sums, double-buffered by batch
+    float* s_old = s_part + 2 * FA_WARPS;                            // [K_TR] dequantised old v_row of the strip's rows
 
     const int strip = w.tile;
     const int row0 = strip * K_TR;
@@ -123,17 +111,9 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
     const unsigned char* g_src = reinterpret_cast<const unsigned char*>(d.g);
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < nstages; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], WPG); }
+        for (int i = 0; i < nstages; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], FA_WARPS); }
         sh->abort = 0;
         mbar_init_fence();
-    }
-    // old second-moment state of the strip's rows, fetched once (a dependent global load per batch would sit on
-    // every warp's critical path)
-    if (threadIdx.x < nrows) {
-        const int row = row0 + threadIdx.x;
-        s_old[threadIdx.x] = d.mode != CAME_MODE_FP32
-            ? (float)reinterpret_cast<const uint8_t*>(d.sq_row)[row] * (d.sq_row_absmax[row >> 8] / QMAX_U8)
-            : reinterpret_cast<const float*>(d.sq_row)[row];
     }
     __syncthreads();
 
@@ -153,145 +133,160 @@ __global__ void __launch_bounds__(FA_THREADS + 32, 1) k_sqstat_fused(StepArgs a,
         return;
     }
 
-    const int group = threadIdx.x / GT, tig = threadIdx.x - group * GT, wig = warp - group * WPG;
-    // this thread's column groups: 8 consecutive columns starting at 8 * (tig + GT * j)
+    // old second-moment state of the strip's rows, fetched once while the first copies are in flight (a dependent
+    // global load per batch would sit on every warp's critical path)
+    if (threadIdx.x < nrows) {
+        const int row = row0 + threadIdx.x;
+        s_old[threadIdx.x] = d.mode != CAME_MODE_FP32
+            ? (float)reinterpret_cast<const uint8_t*>(d.sq_row)[row] * (d.sq_row_absmax[row >> 8] / QMAX_U8)
+            : reinterpret_cast<const float*>(d.sq_row)[row];
+    }
+    named_sync(1, FA_THREADS);
+
+    // row sweep: this warp's row of a batch and its span of 8-column groups within the row
+    const int ncg = C >> 3;                      // 8-column groups per row
+    const int ppr = FA_WARPS / rb;               // pieces per row (rb is a power of two <= 16)
+    const int my_row = warp / ppr, my_piece = warp - my_row * ppr;
+    const int cg_lo = (int)((int64_t)my_piece * ncg / ppr), cg_hi = (int)((int64_t)(my_piece + 1) * ncg / ppr);
+    const int piece_chunks = (cg_hi - cg_lo) >> 5, piece_rem = (cg_hi - cg_lo) & 31;
+    // column sweep: row set (RS = 2: even / odd rows) and 8-column groups of this thread
+    constexpr int ST = FA_THREADS / RS;          // threads of a row set
+    const int rset = threadIdx.x / ST, tis = threadIdx.x - rset * ST;
+    // a thread whose group lies beyond the last column sweeps group 0 instead and drops the result: the sweep
+    // itself then needs no per-group test
     bool gvalid[NG];
+    int coff[NG];
     u64 colb[NG][4], colT[NG][4];
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
-        gvalid[j] = (tig + GT * j) * 8 < C;
+        gvalid[j] = tis + ST * j < ncg;
+        coff[j] = (gvalid[j] || NG > 2) ? (tis + ST * j) * 8 : 0;
 #pragma unroll
         for (int e = 0; e < 4; ++e) { colb[j][e] = F2ZERO; colT[j][e] = F2ZERO; }
     }
-    bool ok = true;
-    int nb_done = 0;       // batches this group has gone through (selects the s_part buffer)
 
-    int slot = group;      // ring position of batch b, advanced without a division (GROUPS <= slots)
-    uint32_t phase = 0;
-    for (int b = group; b < nbatch; b += GROUPS, ++nb_done, slot += GROUPS) {
-        if (slot >= nstages) { slot -= nstages; phase ^= 1u; }
-        // After a failed wait a warp keeps walking its batches without touching data, so that it still meets
-        // the other warps of its group at the hardware barrier below once per batch (nobody is left waiting).
-        if (ok && !fa_wait(&sh->full[slot], phase, sh, a, lane)) ok = false;
-        if (!ok) { named_sync(1 + group, GT); continue; }
+    auto row_sweep = [&](int b, int slot, float* part) {
+        const int rows = min(rb, nrows - b * rb);
+        float t = 0.0f;
+        if (my_row < rows) {
+            const TG* src = reinterpret_cast<const TG*>(smem + slot * stage_bytes + my_row * row_bytes);
+            u64 acc[4] = {F2ZERO, F2ZERO, F2ZERO, F2ZERO};
+            // whole 32-group chunks without a per-lane test, then the ragged end of the piece
+            const TG* p = src + (cg_lo + lane) * 8;
+#pragma unroll 4
+            for (int i = 0; i < piece_chunks; ++i, p += 256) {
+                u64 g2[4];
+                smem_run8(p, g2);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] = fma2(g2[e], g2[e], acc[e]);
+            }
+            if (lane < piece_rem) {
+                u64 g2[4];
+                smem_run8(p, g2);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[e] = fma2(g2[e], g2[e], acc[e]);
+            }
+            const u64 q = add2(add2(acc[0], acc[1]), add2(acc[2], acc[3]));
+            t = q.x + q.y;
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+        if (lane == 0) part[warp] = t;
+    };
+    // completes the row sums of batch b (each warp for itself, lane r: row r, so no second barrier is needed; warp 0
+    // publishes v_row), then the column sweep.  Mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with
+    // the old state.
+    auto col_sweep = [&](int b, int slot, const float* part) {
         const int rows = min(rb, nrows - b * rb);
         const unsigned char* st = smem + slot * stage_bytes;
-        float* part = s_part + (nb_done & 1) * (FA_WARPS * 4) + group * (WPG * 4);
-
-        // sweep 1: row sums and column sums of g^2.  Row partials stay in registers (static indices: the loops
-        // are fully unrolled and guarded) and are reduced across the warp together.
-        float rp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        u64 sqk[KEEP ? RBM : 1][KEEP ? NG : 1][4];      // KEEP: g^2 of this thread's elements, reused by sweep 2
-#pragma unroll
-        for (int r = 0; r < RBM; ++r) {
-            if (KEEP) {
-#pragma unroll
-                for (int j = 0; j < NG; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sqk[KEEP ? r : 0][KEEP ? j : 0][e] = F2ZERO;
-            }
-            if (r < rows) {
-                u64 racc = F2ZERO;
-#pragma unroll
-                for (int j = 0; j < NG; ++j) {
-                    if (gvalid[j]) {
-                        u64 g2[4];
-                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (tig + GT * j) * 8, g2);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            if (KEEP) {
-                                const u64 sq = mul2(g2[e], g2[e]);
-                                sqk[KEEP ? r : 0][KEEP ? j : 0][e] = sq;
-                                colb[j][e] = add2(colb[j][e], sq);
-                                racc = add2(racc, sq);
-                            } else {
-                                colb[j][e] = fma2(g2[e], g2[e], colb[j][e]);
-                                racc = fma2(g2[e], g2[e], racc);
-                            }
-                        }
-                    }
-                }
-                rp[r] = racc.x + racc.y;
-            }
-        }
-        if (KEEP) {      // the slot's bytes are in registers: hand it back before the barrier
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->empty[slot]);
-        }
-        {
-            const float t = warp_reduce_rows<4>(rp, lane);
-            if ((lane & 7) == 0) part[wig * 4 + ((lane >> 3) & 3)] = t;
-        }
-        // barrier among the warps of this group: the per-warp row partials of the batch are complete
-        named_sync(1 + group, GT);
-
-        // every warp finishes the row sums itself (lane r: row r), so no second barrier is needed; the group's first
-        // warp publishes v_row.  Mean of g^2 + eps0 over the row (came_kernels.cu:77-88), EMA with the old state.
         float wrow = 0.0f;
         if (lane < rows) {
             float sum = 0.0f;
-#pragma unroll
-            for (int ww = 0; ww < WPG; ++ww) sum += part[ww * 4 + lane];
+            for (int q = 0; q < ppr; ++q) sum += part[lane * ppr + q];
             const int row = row0 + b * rb + lane;
-            const float mean = (sum + (float)C * h.eps0) / (float)C;
-            const float v = s_old[b * rb + lane] * h.beta2 + h.om_beta2 * mean;
-            if (wig == 0) s.vr[row] = v;
+            const float mean = (sum + eps0C) / fC;
+            const float v = s_old[b * rb + lane] * beta2 + om_beta2 * mean;
+            if (warp == 0) vr[row] = v;
             wrow = v > 0.0f ? 1.0f / v : 0.0f;
         }
-        // sweep 2: column sums of g^2 / v_row
+        // rows of this thread's set; the trip count is uniform across the warp, so the shuffle is converged
+        const TG* src = reinterpret_cast<const TG*>(st + rset * row_bytes);
+#pragma unroll 2
+        for (int r = rset; r < rows; r += RS, src += RS * C) {
+            const u64 w2 = splat(__shfl_sync(0xffffffffu, wrow, r));
 #pragma unroll
-        for (int r = 0; r < RBM; ++r) {
-            if (r < rows) {
-                const u64 w2 = splat(__shfl_sync(0xffffffffu, wrow, r));
+            for (int j = 0; j < NG; ++j) {
+                if (NG <= 2 || gvalid[j]) {      // wide rows keep the test: without it the offsets cost registers they lack
+                    u64 g2[4];
+                    smem_run8(src + coff[j], g2);
 #pragma unroll
-                for (int j = 0; j < NG; ++j) {
-                    if (KEEP) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) colT[j][e] = fma2(sqk[KEEP ? r : 0][KEEP ? j : 0][e], w2, colT[j][e]);
-                    } else if (gvalid[j]) {
-                        u64 g2[4];
-                        smem_run8(reinterpret_cast<const TG*>(st + r * row_bytes) + (tig + GT * j) * 8, g2);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) colT[j][e] = fma2(mul2(g2[e], g2[e]), w2, colT[j][e]);
+                    for (int e = 0; e < 4; ++e) {
+                        const u64 sq = mul2(g2[e], g2[e]);
+                        colb[j][e] = add2(colb[j][e], sq);
+                        colT[j][e] = fma2(sq, w2, colT[j][e]);
                     }
                 }
             }
         }
-        if (!KEEP) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->empty[slot]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->empty[slot]);
+    };
+
+    // After a failed wait a warp keeps walking its batches without touching data, so that it still meets the
+    // other warps at the hardware barrier once per batch (nobody is left waiting).
+    bool ok = true;
+    int slot = 0;      // ring position advanced without a division
+    uint32_t phase = 0;
+    float* part_cur = s_part;
+    float* part_nxt = s_part + FA_WARPS;
+    if (fa_wait(&sh->full[0], 0, sh, a, lane)) row_sweep(0, 0, part_cur);
+    else ok = false;
+    named_sync(1, FA_THREADS);
+    for (int b = 0; b < nbatch; ++b) {
+        int nslot = slot + 1;
+        uint32_t nphase = phase;
+        if (nslot == nstages) { nslot = 0; nphase ^= 1u; }
+        if (ok && b + 1 < nbatch) {
+            if (fa_wait(&sh->full[nslot], nphase, sh, a, lane)) row_sweep(b + 1, nslot, part_nxt);
+            else ok = false;
         }
+        if (ok) col_sweep(b, slot, part_cur);
+        named_sync(1, FA_THREADS);
+        slot = nslot; phase = nphase;
+        float* t = part_cur; part_cur = part_nxt; part_nxt = t;
     }
     if (!ok) return;      // the status word is set; the partial sums of this strip stay unwritten
-    // one set of column partials per (strip, group)
+    // one set of column partials per (strip, row set)
 #pragma unroll
     for (int j = 0; j < NG; ++j) {
         if (gvalid[j]) {
-            const int64_t off = (int64_t)(strip * GROUPS + group) * C + (tig + GT * j) * 8;
-            reinterpret_cast<float4*>(s.colpart + off)[0] = make_float4(colb[j][0].x, colb[j][0].y, colb[j][1].x, colb[j][1].y);
-            reinterpret_cast<float4*>(s.colpart + off)[1] = make_float4(colb[j][2].x, colb[j][2].y, colb[j][3].x, colb[j][3].y);
-            reinterpret_cast<float4*>(s.tpart + off)[0] = make_float4(colT[j][0].x, colT[j][0].y, colT[j][1].x, colT[j][1].y);
-            reinterpret_cast<float4*>(s.tpart + off)[1] = make_float4(colT[j][2].x, colT[j][2].y, colT[j][3].x, colT[j][3].y);
+            const int64_t off = (int64_t)(strip * RS + rset) * C + coff[j];
+            reinterpret_cast<float4*>(colpart + off)[0] = make_float4(colb[j][0].x, colb[j][0].y, colb[j][1].x, colb[j][1].y);
+            reinterpret_cast<float4*>(colpart + off)[1] = make_float4(colb[j][2].x, colb[j][2].y, colb[j][3].x, colb[j][3].y);
+            reinterpret_cast<float4*>(tpart + off)[0] = make_float4(colT[j][0].x, colT[j][0].y, colT[j][1].x, colT[j][1].y);
+            reinterpret_cast<float4*>(tpart + off)[1] = make_float4(colT[j][2].x, colT[j][2].y, colT[j][3].x, colT[j][3].y);
         }
     }
 }
 
 // Geometry of the fused first pass for a matrix of `cols` columns of `elem_bytes` each:
-//   groups   2 up to 2048 columns (two 8-warp groups on alternate batches), else 1
-//   ng       column groups of 8 per thread within its group (1..4)
-//   rb       rows per staged batch: at most 4/ng while the squares are kept in registers (ng <= 2), at most 4
-//            otherwise, and never more than fit 64 KB
-//   stages   ring slots: as many as fit ~160 KB, between 3 and 8
+//   groups   row sets of the column sweep: 2 up to 2048 columns, else 1
+//   ng       8-column groups per thread in the column sweep (1..4)
+//   rb       rows per staged batch: the largest power of two that fits 64 KB, between 1 and 16 (the cost of a
+//            batch is mostly fixed, so large batches pay)
+//   stages   ring slots: as many as fit 192 KB, between 3 and 8 (a computing warp holds two at a time)
 void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb, int* stages) {
-    const int g = cols <= (int64_t)FA_THREADS * 4 ? 2 : 1;
-    const int gt = FA_THREADS / g;
-    const int n = (int)((cols / 8 + gt - 1) / gt);
+    const int64_t ncg = cols / 8;
+    const int g = ncg <= FA_THREADS / 2 ? 2 : 1;
+    const int n = g == 2 ? 1 : (int)((ncg + FA_THREADS - 1) / FA_THREADS);
     const int64_t row_bytes = cols * elem_bytes;
-    int64_t r = (64 * 1024) / row_bytes;
-    const int64_t cap = n <= 2 ? 4 / n : 4;
-    if (r > cap) r = cap;
-    if (r < 1) r = 1;
-    int64_t st = (160 * 1024) / (r * row_bytes);
+    int64_t r = 1;
+    while (r < FA_RB && 2 * r * row_bytes <= 64 * 1024) r *= 2;
+    int64_t st = (192 * 1024) / (r * row_bytes);
+#ifdef CAME_TUNE      // build-time experiment switch: geometry overrides from the environment
+    if (const char* e = getenv("CAME_FA_RB")) { r = atoi(e); while (r > 1 && r * row_bytes > 64 * 1024) r /= 2; st = (192 * 1024) / (r * row_bytes); }
+    if (const char* e = getenv("CAME_FA_STAGES")) st = std::min<int64_t>(st, atoi(e));
+#endif
     if (st > FA_MAX_STAGES) st = FA_MAX_STAGES;
     if (st < 3) st = 3;
     *groups = g; *ng = n < 1 ? 1 : n; *rb = (int)r; *stages = (int)st;
@@ -325,7 +320,7 @@ static cudaError_t launch_ng(int ng, int groups, const StepArgs& a, const Work* 
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, size_t max_ring_bytes,
                             cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
-    const size_t smem = max_ring_bytes + sizeof(FaShared) + (2 * FA_WARPS * 4 + K_TR) * sizeof(float);
+    const size_t smem = max_ring_bytes + sizeof(FaShared) + (2 * FA_WARPS + K_TR) * sizeof(float);
     const int ng = key.mode & 15, groups = key.mode >> 4;
     switch (key.g_dtype) {
         case CAME_DT_F32: return launch_ng<float>(ng, groups, a, work, n, smem, st);
