@@ -129,7 +129,10 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.colpart = take((size_t)std::max(s.sq_col_parts, g.ptiles_r) * (size_t)g.C);
         s.spart = take(std::max((size_t)g.tiles_r * (size_t)g.tiles_c, (size_t)g.nbC));
         s.fac = (d.mode == CAME_MODE_FLAT8 && vec_flags(d).flat != 2) ? take(2 * (size_t)(g.R + g.C)) : nullptr;
-        if (vec_flags(d).p2 == 2) s.res_eps_deferred = 1;
+        if (vec_flags(d).p2 == 2) {
+            s.res_eps_deferred = 1;
+            s.mfac = take((size_t)(g.R + g.C));
+        }
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
             s.fa_rb = fa_rb;
@@ -346,7 +349,11 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
     build(KID_SUMSQ, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
-    build(KID_S_FINALIZE, is2d, nokey, [&](int) { return (int64_t)1; });
+    // one CTA per tensor for the clip scalar; tensors of the staged momentum pass get one CTA per 2048 entries of
+    // their factor vectors (each CTA repeats the cheap scalar part)
+    build(KID_S_FINALIZE, is2d, nokey, [&](int i) {
+        return vf[i].p2 == 2 ? std::max<int64_t>(1, cdiv(D[i].rows + D[i].cols, S_FIN_CHUNK)) : (int64_t)1;
+    });
     build(KID_MOMENT, is2d, [&](int i) { return Key{D[i].g_dtype, 0, D[i].mode, vf[i].p2}; },
           [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
     build(KID_RES_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });

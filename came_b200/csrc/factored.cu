@@ -237,11 +237,22 @@ __global__ void __launch_bounds__(THREADS) k_s_finalize(StepArgs a, const Work* 
     } else {
         S = block_vector_sum(s.spart, s.tiles_r * s.tiles_c, red);
     }
-    if (threadIdx.x == 0) {
-        const float n = (float)((int64_t)d.rows * d.cols);
-        const float rms = sqrtf(S / n);
+    const float n = (float)((int64_t)d.rows * d.cols);
+    const float clip = fmaxf(1.0f, sqrtf(S / n) / a.hyp[d.group].clip_threshold);   // S is the same in every thread
+    if (threadIdx.x == 0 && w.tile == 0) {
         s.scal[0] = S;
-        s.scal[1] = fmaxf(1.0f, rms / a.hyp[d.group].clip_threshold);
+        s.scal[1] = clip;
+    }
+    if (s.mfac) {
+        // factor vectors of the momentum pass, once per tensor instead of once per tile: r_i / clip, then c_j
+        const bool clamp = d.flags & CAME_F_SQ_CLAMP;
+        float mean = block_vector_sum(s.rowblk, s.nbR, red) / (float)d.rows;
+        mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
+        const float inv_clip = 1.0f / clip;
+        const int R = (int)d.rows, C = (int)d.cols;
+        const int hi = min(R + C, (w.tile + 1) * S_FIN_CHUNK);      // this CTA's chunk of the R + C entries
+        for (int i = w.tile * S_FIN_CHUNK + threadIdx.x; i < hi; i += THREADS)
+            s.mfac[i] = i < R ? row_factor(s.vr[i], mean, clamp) * inv_clip : col_factor(s.vc[i - R], clamp);
     }
 }
 

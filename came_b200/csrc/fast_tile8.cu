@@ -229,14 +229,27 @@ __device__ __forceinline__ float warp_vector_sum(const float* x, int n, int lane
 // 256 consecutive elements = per 256-column row segment, the column count being a multiple of 256): only the
 // residual sums are produced; the flat apply pass recomputes the momentum so that its un-quantised value feeds
 // the update (came_kernels.cu:2246-2305 keeps it in fp32 scratch instead).
+// What the computing warps need to know about a work item, prepared in shared memory by the helper warp while
+// the previous item is being computed (reading it from the tables in global memory would put a chain of
+// dependent loads at the start of every item, which the computing warps cannot hide).
+struct MomentItem {
+    int8_t* m;              // codes of the tensor
+    float* m_absmax;
+    float* colpart;
+    int R, C, row0, col0, wcols, nbands, tr, pad;
+    float om_beta1, dq_beta1;     // 1 - beta1;  beta1 / 127
+};
+
 template <typename TG, bool FLAT>
-__global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+__global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
     constexpr int STAGES = WideCfg<TG>::STAGES, STAGE = WideCfg<TG>::STAGE, ROW = WideCfg<TG>::ROW;
+    constexpr int ITEM_SYNC = W_CONSUMERS + 32;          // the computing warps and the helper warp
     extern __shared__ __align__(128) unsigned char smem[];
     WideShared* sh = reinterpret_cast<WideShared*>(smem + STAGES * STAGE);
     float* s_r = reinterpret_cast<float*>(sh + 1);      // [2][W_TR]   row factors (times 1/clip), double-buffered by item
     float* s_c = s_r + 2 * W_TR;                        // [2][W_TC]   column factors
     float* s_row = s_c + 2 * W_TC;                      // [2][W_WARPS][W_TR]  per-warp row partials of the residual
+    MomentItem* s_item = reinterpret_cast<MomentItem*>(s_row + 2 * W_WARPS * W_TR);    // [2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -251,6 +264,53 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         while (prod.live && prod.issue(a, work, n_items, true, smem, sh, lane)) {}
         return;
     }
+    if (warp == W_WARPS + 1) {
+        // Helper warp.  Between the barriers of items i and i+1 (while the computing warps run item i) it finishes
+        // item i-1 (sums its per-warp row partials in a fixed order) and prepares item i+1 (its slices of the
+        // tensor's factor vectors and the item record).  It takes part in every item
+        // barrier and waits for nothing else, so it cannot be the reason a barrier does not complete.
+        auto prepare = [&](int item, int buf) {
+            const WideItem it = wide_item<TG>(a, work[item], true);
+            const CameTensorDesc& d = a.descs[it.tensor];
+            const Scratch& s = a.scr[it.tensor];
+            const CameHyper& h = a.hyp[d.group];
+            float* sr = s_r + buf * W_TR;
+            float* sc = s_c + buf * W_TC;
+            const float* fr = s.mfac + it.row0;              // r_i / clip, prepared once per tensor by k_s_finalize
+            const float* fc = s.mfac + it.R + it.col0;       // c_j
+            for (int i = lane; i < W_TR; i += 32) sr[i] = (it.row0 + i < it.R) ? fr[i] : 0.0f;
+            for (int i = lane; i < it.wcols; i += 32) sc[i] = fc[i];
+            if (lane == 0) {
+                MomentItem& mi = s_item[buf];
+                mi.m = reinterpret_cast<int8_t*>(d.m); mi.m_absmax = d.m_absmax; mi.colpart = s.colpart;
+                mi.R = it.R; mi.C = it.C; mi.row0 = it.row0; mi.col0 = it.col0; mi.wcols = it.wcols;
+                mi.nbands = it.nbands; mi.tr = it.tr;
+                mi.om_beta1 = h.om_beta1; mi.dq_beta1 = h.beta1 / QMAX_I8;
+            }
+        };
+        auto row_epilogue = [&](int item, int buf) {
+            const WideItem it = wide_item<TG>(a, work[item], true);
+            float* rowpart = a.scr[it.tensor].rowpart;
+            const float* prow = s_row + buf * (W_WARPS * W_TR);
+            const int nw = (it.wcols + 63) >> 6, nrows = min(W_TR, it.R - it.row0);
+            for (int i = lane; i < nrows; i += 32) {
+                float t = 0.0f;
+                for (int ww = 0; ww < nw; ++ww) t += prow[ww * W_TR + i];
+                rowpart[(int64_t)it.tc * it.R + it.row0 + i] = t;
+            }
+        };
+        int item = blockIdx.x, buf = 0;
+        if (item < n_items) prepare(item, 0);
+        for (; item < n_items; item += gridDim.x, buf ^= 1) {
+            named_sync(1, ITEM_SYNC);                   // item barrier: `item` starts, item - grid is complete
+            if (*reinterpret_cast<volatile int*>(&sh->abort)) continue;
+            if (item != (int)blockIdx.x) row_epilogue(item - gridDim.x, buf ^ 1);
+            if (item + (int)gridDim.x < n_items) prepare(item + gridDim.x, buf ^ 1);
+        }
+        named_sync(1, ITEM_SYNC);                       // the last item is complete
+        if (item != (int)blockIdx.x && !*reinterpret_cast<volatile int*>(&sh->abort)) row_epilogue(item - gridDim.x, buf ^ 1);
+        return;
+    }
     const int c8 = lane & 7, rsub = lane >> 3;
     const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
     const u64 magic = splat(ROUND_MAGIC);
@@ -261,51 +321,28 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
     long long prof_issue = 0, prof_wait = 0, prof_bar = 0;
     const long long prof_start = clock64();
 #endif
-    // epilogue of the previous item, finished after the next item's barrier (s_row is complete only then)
-    int prev_valid = 0, prev_row0 = 0, prev_R = 0, prev_tc = 0, prev_nw = 0, prev_nrows = 0;
-    float* prev_rowpart = nullptr;
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, buf ^= 1) {
-        const WideItem it = wide_item<TG>(a, work[item], true);
-        const CameTensorDesc& d = a.descs[it.tensor];
-        const Scratch& s = a.scr[it.tensor];
-        const CameHyper& h = a.hyp[d.group];
-        const int R = it.R, C = it.C;
-        const bool active = cl < it.wcols;        // warps beyond a ragged tile width idle
-        const int col = it.col0 + cl;
-        const int tile_cols = C >> 4;
-        float* sr = s_r + buf * W_TR;
-        float* sc = s_c + buf * W_TC;
-        float* srow = s_row + buf * (W_WARPS * W_TR);
-        if (!aborted) {   // row / column factors of this tile (same arithmetic as stage_factors in factored.cu)
-            const bool clamp = d.flags & CAME_F_SQ_CLAMP;
-            float mean = warp_vector_sum(s.rowblk, s.nbR, lane) / (float)R;
-            mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
-            const float inv_clip = 1.0f / s.scal[1];
-            for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS)
-                sr[i] = (it.row0 + i < R) ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
-            for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS) sc[i] = col_factor(s.vc[it.col0 + i], clamp);
-        }
         {
-            // also: every warp has finished the previous item, whose row partials are complete now.  A warp that
-            // gave up a wait still comes here once per item (see below), so this hardware barrier cannot hang.
+            // Item barrier: every warp has finished the previous item and the helper has prepared this one.  A warp
+            // that gave up a wait still comes here once per item (see below), so this hardware barrier cannot hang.
 #ifdef CAME_WIDE_PROFILE
             const long long tb = clock64();
 #endif
-            named_sync(1, W_CONSUMERS);
+            named_sync(1, ITEM_SYNC);
 #ifdef CAME_WIDE_PROFILE
             prof_bar += clock64() - tb;
 #endif
             if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) { aborted = true; continue; }
         }
-        if (prev_valid) {   // row partials of the previous item: sum the per-warp shares in a fixed order
-            const float* prow = s_row + (buf ^ 1) * (W_WARPS * W_TR);
-            for (int i = threadIdx.x; i < prev_nrows; i += W_CONSUMERS) {
-                float t = 0.0f;
-                for (int ww = 0; ww < prev_nw; ++ww) t += prow[ww * W_TR + i];
-                prev_rowpart[(int64_t)prev_tc * prev_R + prev_row0 + i] = t;
-            }
-        }
+        const MomentItem& mi = s_item[buf];
+        const int R = mi.R, C = mi.C, row0 = mi.row0, nbands = mi.nbands;
+        const bool active = cl < mi.wcols;        // warps beyond a ragged tile width idle
+        const int col = mi.col0 + cl;
+        const int tile_cols = C >> 4;
+        const float* sr = s_r + buf * W_TR;
+        const float* sc = s_c + buf * W_TC;
+        float* srow = s_row + buf * (W_WARPS * W_TR);
         u64 cf2[4], colacc[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -314,27 +351,30 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
         }
         // old tile absmax, fetched one band ahead: a dependent global load at the top of every band would sit
         // on the critical path of the iteration
-        const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
-        float a_next = (active && !FLAT) ? amax_col[0] : 0.0f;
         // flat layout: one absmax per (row, 256-column segment); this lane's 4 rows of the band, one band ahead
-        const float* amax_flat = d.m_absmax + (((int64_t)(it.row0 + rsub) * C + col) >> 8);
+        const float* amax_flat = mi.m_absmax + (((int64_t)(row0 + rsub) * C + col) >> 8);
         const int64_t flat_row_step = C >> 8;       // absmax entries per row
         float af_next[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (FLAT && active) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                if (it.row0 + rsub + 4 * i < R) af_next[i] = amax_flat[(int64_t)(4 * i) * flat_row_step];
+                if (row0 + rsub + 4 * i < R) af_next[i] = amax_flat[(int64_t)(4 * i) * flat_row_step];
         }
-        const u64 om2 = splat(h.om_beta1);
-        const float beta1 = h.beta1;
-        // table entries the band loop uses, read once per item (the barriers in the loop make the compiler reload them)
-        int8_t* const m_base = reinterpret_cast<int8_t*>(d.m);
-        float* const m_absmax = d.m_absmax;
-        float* const colpart = s.colpart;
+        const u64 om2 = splat(mi.om_beta1);
+        // old code -> beta1 * (code * absmax / 127) as one scale per tile: absmax * (beta1 / 127)
+        const float dq_beta1 = mi.dq_beta1;
+        // Pointers that walk down the tile one band at a time (one 64-bit add per band instead of index arithmetic
+        // from the table entries, which the barriers in the loop would make the compiler reload on every band)
+        int8_t* mdst = mi.m + (int64_t)(row0 + rsub) * C + col;                               // this lane's first row
+        float* amax_dst = mi.m_absmax + (int64_t)(row0 >> 4) * tile_cols + (col >> 4);        // this lane's tile
+        const int64_t band_bytes = (int64_t)W_BAND * C;
+        float a_next = (active && !FLAT) ? amax_dst[0] : 0.0f;
+        const float* sr_k = sr + rsub;                                                         // row factors of the band
+        float* srow_k = srow + warp * W_TR + rsub;
         bool ok = true;
 
 #pragma unroll 1
-        for (int k = 0; k < it.nbands; ++k, ++q) {
+        for (int k = 0; k < nbands; ++k, ++q) {
             const int slot = q % STAGES;
 #ifdef CAME_WIDE_PROFILE
             const long long t0 = clock64(), t1 = t0;
@@ -347,15 +387,14 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             if (!active) { wide_release(sh, slot, lane); continue; }
             const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(TG);
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
-            const int brow = it.row0 + k * W_BAND;
-            const int64_t tile_id = (int64_t)(brow >> 4) * tile_cols + (col >> 4);
+            const int brow = row0 + k * W_BAND;
             const float a_old = a_next;
-            if (!FLAT && k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
-            const u64 scb2 = splat(a_old > 0.0f ? (a_old / QMAX_I8) * beta1 : 0.0f);
+            if (!FLAT && k + 1 < nbands) a_next = amax_dst[tile_cols];
+            const u64 scb2 = splat(a_old * dq_beta1);      // a tile that was never written has absmax 0: scale 0
             float af[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) af[i] = af_next[i];
-            if (FLAT && k + 1 < it.nbands) {
+            if (FLAT && k + 1 < nbands) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                     if (brow + W_BAND + rsub + 4 * i < R)
@@ -379,8 +418,8 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                     wide_run8(reinterpret_cast<const TG*>(sg + r * ROW), g2);
                     uint2 mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
                     mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
-                    const u64 ra2 = splat(live ? sr[k * W_BAND + r] : 0.0f);
-                    const u64 sc_row2 = FLAT ? splat((af[i] / QMAX_I8) * beta1) : scb2;
+                    const u64 ra2 = splat(live ? sr_k[4 * i] : 0.0f);
+                    const u64 sc_row2 = FLAT ? splat(af[i] * dq_beta1) : scb2;
                     u64 rs2 = F2ZERO;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -406,7 +445,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
                 A = fix_absmax(amax);
-                int8_t* mdst = m_base + (int64_t)(brow + rsub) * C + col;
                 // the reciprocal form needs a normal 1/A: decided per warp so that the branch never diverges
                 if (__all_sync(0xffffffffu, recip_safe(A))) {
                     // code = rint((m / A) * 127) computed as rint(m * (127 / A)) in one FMA with the rounding constant:
@@ -440,7 +478,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             };
             if (full_band) band(std::true_type{});
             else band(std::false_type{});
-            if (!FLAT && rsub == 0 && (c8 & 1) == 0) m_absmax[tile_id] = A;     // one lane per tile
+            if (!FLAT && rsub == 0 && (c8 & 1) == 0) *amax_dst = A;     // one lane per tile
             // row sums over this warp's 64 columns: halving butterfly over the 8 column groups (4 shuffles instead
             // of 12); lane c8 ends up with the sum of row rsub + 4 * ((c8 >> 1) & 3) when c8 is even
             {
@@ -450,8 +488,9 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 float v = (up2 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, up2 ? a0 : a1, 2);
                 v += __shfl_xor_sync(0xffffffffu, v, 1);
                 const int irow = (up4 ? 2 : 0) + (up2 ? 1 : 0);
-                if ((c8 & 1) == 0) srow[warp * W_TR + k * W_BAND + rsub + 4 * irow] = v;
+                if ((c8 & 1) == 0) srow_k[4 * irow] = v;
             }
+            mdst += band_bytes; amax_dst += tile_cols; sr_k += W_BAND; srow_k += W_BAND;
         }
         if (!ok) { aborted = true; continue; }
         // column partials: the 4 row groups of a warp hold partial sums of the same 8 columns
@@ -462,31 +501,18 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 upk(colacc[j], lo, hi);
                 lo += __shfl_xor_sync(0xffffffffu, lo, 8);  hi += __shfl_xor_sync(0xffffffffu, hi, 8);
                 lo += __shfl_xor_sync(0xffffffffu, lo, 16); hi += __shfl_xor_sync(0xffffffffu, hi, 16);
-                if (rsub == 0) *reinterpret_cast<float2*>(colpart + (int64_t)it.tr * C + col + 2 * j) = make_float2(lo, hi);
+                if (rsub == 0) *reinterpret_cast<float2*>(mi.colpart + (int64_t)mi.tr * C + col + 2 * j) = make_float2(lo, hi);
             }
         }
-        prev_valid = 1; prev_row0 = it.row0; prev_R = R; prev_tc = it.tc; prev_nw = (it.wcols + 63) >> 6;
-        prev_nrows = min(W_TR, R - it.row0); prev_rowpart = s.rowpart;
     }
 #ifdef CAME_WIDE_PROFILE
     if ((blockIdx.x == 0 || blockIdx.x == 77) && lane == 0 && (warp == 0 || warp == 5 || warp == 15))
         printf("moment cta %d warp %d: total %lld issue %lld wait_full %lld item_barrier %lld bands %d\n", blockIdx.x, warp,
                clock64() - prof_start, prof_issue, prof_wait, prof_bar, q);
 #endif
-    // after this barrier the last item's row partials are complete
-    named_sync(1, W_CONSUMERS);
-    if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) {
-        if (warp == 0) wide_drain(sh, STAGES);
-        return;
-    }
-    if (prev_valid) {
-        const float* prow = s_row + (buf ^ 1) * (W_WARPS * W_TR);
-        for (int i = threadIdx.x; i < prev_nrows; i += W_CONSUMERS) {
-            float t = 0.0f;
-            for (int ww = 0; ww < prev_nw; ++ww) t += prow[ww * W_TR + i];
-            prev_rowpart[(int64_t)prev_tc * prev_R + prev_row0 + i] = t;
-        }
-    }
+    // after this barrier the last item's row partials are complete (the helper warp sums them)
+    named_sync(1, ITEM_SYNC);
+    if ((aborted || *reinterpret_cast<volatile int*>(&sh->abort)) && warp == 0) wide_drain(sh, STAGES);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -807,7 +833,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
 // ------------------------------------------------------------------------------------------------
 template <typename T> static constexpr size_t moment_smem() {
     return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + sizeof(WideShared) +
-           2 * (W_TR + W_TC + W_WARPS * W_TR) * sizeof(float);
+           2 * (W_TR + W_TC + W_WARPS * W_TR) * sizeof(float) + 2 * sizeof(MomentItem);
 }
 template <typename T> static constexpr size_t apply_smem() {
     return (size_t)WideCfg<T>::STAGES * WideCfg<T>::STAGE + sizeof(WideShared) + 2 * (W_TR + W_TC) * sizeof(float);
@@ -818,7 +844,8 @@ template <typename T> static constexpr size_t flat_smem() {
 }
 
 template <typename K>
-static cudaError_t launch_persistent(K kernel, size_t smem, const StepArgs& a, const Work* work, int n, cudaStream_t st) {
+static cudaError_t launch_persistent(K kernel, size_t smem, const StepArgs& a, const Work* work, int n, cudaStream_t st,
+                                     int threads = W_ALL_THREADS) {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -828,7 +855,7 @@ static cudaError_t launch_persistent(K kernel, size_t smem, const StepArgs& a, c
     }
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    kernel<<<n < sms ? n : sms, W_ALL_THREADS, smem, st>>>(a, work, n);
+    kernel<<<n < sms ? n : sms, threads, smem, st>>>(a, work, n);
     return cudaGetLastError();
 }
 
@@ -838,15 +865,15 @@ cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& 
     if (kernel == KID_MOMENT) {
         if (key.mode == CAME_MODE_FLAT8) {
             switch (key.g_dtype) {
-                case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, true>, moment_smem<float>(), a, work, n, st);
-                case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, true>, moment_smem<__half>(), a, work, n, st);
-                default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, true>, moment_smem<__nv_bfloat16>(), a, work, n, st);
+                case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, true>, moment_smem<float>(), a, work, n, st, W_ALL_THREADS + 32);
+                case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, true>, moment_smem<__half>(), a, work, n, st, W_ALL_THREADS + 32);
+                default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, true>, moment_smem<__nv_bfloat16>(), a, work, n, st, W_ALL_THREADS + 32);
             }
         }
         switch (key.g_dtype) {
-            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, false>, moment_smem<float>(), a, work, n, st);
-            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, false>, moment_smem<__half>(), a, work, n, st);
-            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, false>, moment_smem<__nv_bfloat16>(), a, work, n, st);
+            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, false>, moment_smem<float>(), a, work, n, st, W_ALL_THREADS + 32);
+            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, false>, moment_smem<__half>(), a, work, n, st, W_ALL_THREADS + 32);
+            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, false>, moment_smem<__nv_bfloat16>(), a, work, n, st, W_ALL_THREADS + 32);
         }
     }
     if (kernel == KID_APPLY_FLAT) {
