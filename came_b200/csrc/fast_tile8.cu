@@ -28,7 +28,8 @@ constexpr int W_MROW = W_TC + 64;                // staged row of int8 codes (+6
 
 template <typename T> struct WideCfg {
     static constexpr int ROW = W_TC * (int)sizeof(T);                  // staged row of T
-    static constexpr int STAGE = W_BAND * (ROW + W_MROW);
+    static constexpr int AMAX_OFF = W_BAND * (ROW + W_MROW);           // the band's W_TC / 16 tile absmax values
+    static constexpr int STAGE = AMAX_OFF + (W_TC / TILE) * (int)sizeof(float);
     static constexpr int STAGES = sizeof(T) == 2 ? 4 : 2;
 };
 
@@ -103,7 +104,8 @@ template <> __device__ __forceinline__ u64 round_pair<__half>(u64 v) {
 struct WideItem {
     const unsigned char* a_src;   // operand A (gradient or parameter), first byte of the tile
     const unsigned char* m_src;   // int8 codes, first byte of the tile
-    int64_t a_pitch, m_pitch;
+    const unsigned char* x_src;   // apply pass, tile layout: absmax of the first band's tiles (else null)
+    int64_t a_pitch, m_pitch, x_pitch;
     int tensor, R, C, row0, col0, wcols, nbands, tr, tc;
 };
 
@@ -126,6 +128,10 @@ __device__ __forceinline__ WideItem wide_item(const StepArgs& a, const Work& w, 
     it.a_src = reinterpret_cast<const unsigned char*>(a_is_grad ? d.g : d.p) + (int64_t)it.row0 * it.a_pitch +
                (int64_t)it.col0 * sizeof(TA);
     it.m_src = reinterpret_cast<const unsigned char*>(d.m) + (int64_t)it.row0 * it.m_pitch + it.col0;
+    it.x_pitch = (int64_t)(it.C >> 4) * sizeof(float);
+    it.x_src = (d.mode == CAME_MODE_TILE8 && !a_is_grad)      // the apply pass only: the momentum pass loads it ahead itself
+        ? reinterpret_cast<const unsigned char*>(d.m_absmax) + (int64_t)(it.row0 >> 4) * it.x_pitch + (it.col0 >> 4) * sizeof(float)
+        : nullptr;
     return it;
 }
 
@@ -187,7 +193,11 @@ struct WideProducer {
         }
         const int rows = min(W_BAND, it.R - it.row0 - band * W_BAND);
         const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(TA), m_bytes = (uint32_t)it.wcols;
-        if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (a_bytes + m_bytes));
+        const uint32_t x_bytes = it.x_src ? (uint32_t)(it.wcols >> 4) * sizeof(float) : 0u;   // a multiple of 16: wcols % 64 == 0
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (a_bytes + m_bytes) + x_bytes);
+            if (x_bytes) bulk_g2s(smem + slot * STAGE + WideCfg<TA>::AMAX_OFF, it.x_src + band * it.x_pitch, x_bytes, &sh->full[slot]);
+        }
         __syncwarp();
         const int r = lane & 15;
         if (r < rows) {
@@ -349,8 +359,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
             cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
             colacc[j] = F2ZERO;
         }
-        // old tile absmax, fetched one band ahead: a dependent global load at the top of every band would sit
-        // on the critical path of the iteration
         // flat layout: one absmax per (row, 256-column segment); this lane's 4 rows of the band, one band ahead
         const float* amax_flat = mi.m_absmax + (((int64_t)(row0 + rsub) * C + col) >> 8);
         const int64_t flat_row_step = C >> 8;       // absmax entries per row
@@ -388,6 +396,8 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
             const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(TG);
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
             const int brow = row0 + k * W_BAND;
+            // old absmax of this lane's tile, fetched one band ahead (a dependent global load here would sit on the
+            // critical path)
             const float a_old = a_next;
             if (!FLAT && k + 1 < nbands) a_next = amax_dst[tile_cols];
             const u64 scb2 = splat(a_old * dq_beta1);      // a tile that was never written has absmax 0: scale 0
@@ -552,7 +562,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
         const int R = it.R, C = it.C;
         const bool active = cl < it.wcols;
         const int col = it.col0 + cl;
-        const int tile_cols = C >> 4;
         float* sr = s_r + buf * W_TR;
         float* sc = s_c + buf * W_TC;
         if (!aborted) {
@@ -570,8 +579,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
         u64 cf2[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) cf2[j] = active ? pk(sc[cl + 2 * j], sc[cl + 2 * j + 1]) : F2ZERO;
-        const float* amax_col = d.m_absmax + (int64_t)(it.row0 >> 4) * tile_cols + (col >> 4);
-        float a_next = active ? amax_col[0] : 0.0f;     // tile absmax, fetched one band ahead
         const int wd_mode = h.weight_decay == 0.0f ? 0 : ((d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 3 : 1));
         const u64 dmul2 = splat(h.decay_mul), nwdlr2 = splat(-h.wd_lr), nlr2 = splat(-h.lr);
         TP* const p_base = reinterpret_cast<TP*>(d.p);      // read once per item, not once per band
@@ -586,8 +593,8 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_tile8_wide(StepArgs 
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
             const int brow = it.row0 + k * W_BAND;
             const bool full_band = brow + W_BAND <= R;
-            const float A = a_next;
-            if (k + 1 < it.nbands) a_next = amax_col[(int64_t)(k + 1) * tile_cols];
+            // absmax of this lane's tile: it came with the band
+            const float A = *reinterpret_cast<const float*>(smem + slot * STAGE + WideCfg<TP>::AMAX_OFF + (cl >> 4) * 4);
             const float scl = A > 0.0f ? A / QMAX_I8 : 0.0f;
             // WD: 0 no decay, 1 one rounding, 2 multiply form with a rounding, 3 add form with a rounding.
             // FULL: all 16 rows of the band exist.  Both are uniform over the item, so the inner loops carry no
