@@ -147,6 +147,8 @@ constexpr int W_ALL_THREADS = W_THREADS + 32;     // + the producer warp
 struct WideShared {
     uint64_t full[4];
     uint64_t empty[4];
+    uint64_t ready[2];      // momentum pass: the helper warp has prepared the item of this buffer
+    uint64_t done[2];       // momentum pass: every computing warp has finished the item of this buffer
     int abort;
     int pad;
 };
@@ -253,7 +255,6 @@ struct MomentItem {
 template <typename TG, bool FLAT>
 __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
     constexpr int STAGES = WideCfg<TG>::STAGES, STAGE = WideCfg<TG>::STAGE, ROW = WideCfg<TG>::ROW;
-    constexpr int ITEM_SYNC = W_CONSUMERS + 32;          // the computing warps and the helper warp
     extern __shared__ __align__(128) unsigned char smem[];
     WideShared* sh = reinterpret_cast<WideShared*>(smem + STAGES * STAGE);
     float* s_r = reinterpret_cast<float*>(sh + 1);      // [2][W_TR]   row factors (times 1/clip), double-buffered by item
@@ -264,21 +265,27 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], W_WARPS); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sh->ready[i], 1); mbar_init(&sh->done[i], W_WARPS); }
         sh->abort = 0;
         mbar_init_fence();
     }
     __syncthreads();
+    // No CTA-wide barrier from here on: the warps meet only through the ring and the item barriers below, all with
+    // bounded, abort-aware waits, so a warp that gives up simply leaves and the others follow at their next wait.
     if (warp == W_WARPS) {      // producer warp: run the copy stream as far ahead as the ring allows
         WideProducer<TG> prod;
         prod.init(a, work, n_items, true);
         while (prod.live && prod.issue(a, work, n_items, true, smem, sh, lane)) {}
+        // after a failed wait somewhere in the CTA: let the copies in flight land before shared memory is released
+        if (*reinterpret_cast<volatile int*>(&sh->abort)) wide_drain(sh, STAGES);
         return;
     }
     if (warp == W_WARPS + 1) {
-        // Helper warp.  Between the barriers of items i and i+1 (while the computing warps run item i) it finishes
-        // item i-1 (sums its per-warp row partials in a fixed order) and prepares item i+1 (its slices of the
-        // tensor's factor vectors and the item record).  It takes part in every item
-        // barrier and waits for nothing else, so it cannot be the reason a barrier does not complete.
+        // Helper warp.  Items alternate between two buffers (factor slices, item record, per-warp row partials).
+        // For the n-th item of this CTA the helper waits until every computing warp has finished it (`done`), sums
+        // its per-warp row partials in a fixed order, then prepares item n+2 in the same buffer and publishes it
+        // (`ready`).  The computing warps thus never wait for each other at an item boundary, only for `ready`,
+        // which normally completed a whole item earlier.
         auto prepare = [&](int item, int buf) {
             const WideItem it = wide_item<TG>(a, work[item], true);
             const CameTensorDesc& d = a.descs[it.tensor];
@@ -309,42 +316,31 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
                 rowpart[(int64_t)it.tc * it.R + it.row0 + i] = t;
             }
         };
-        int item = blockIdx.x, buf = 0;
-        if (item < n_items) prepare(item, 0);
-        for (; item < n_items; item += gridDim.x, buf ^= 1) {
-            named_sync(1, ITEM_SYNC);                   // item barrier: `item` starts, item - grid is complete
-            if (*reinterpret_cast<volatile int*>(&sh->abort)) continue;
-            if (item != (int)blockIdx.x) row_epilogue(item - gridDim.x, buf ^ 1);
-            if (item + (int)gridDim.x < n_items) prepare(item + gridDim.x, buf ^ 1);
+        auto publish = [&](int buf) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->ready[buf]);      // release: the writes above are visible to the waiters
+        };
+        for (int j = 0; j < 2; ++j)
+            if ((int)(blockIdx.x + j * gridDim.x) < n_items) { prepare(blockIdx.x + j * gridDim.x, j); publish(j); }
+        int n = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
+            const int buf = n & 1;
+            if (!wide_wait(&sh->done[buf], (n >> 1) & 1, sh, a, lane)) return;
+            row_epilogue(item, buf);
+            const int64_t next = (int64_t)item + 2 * (int64_t)gridDim.x;
+            if (next < n_items) { prepare((int)next, buf); publish(buf); }
         }
-        named_sync(1, ITEM_SYNC);                       // the last item is complete
-        if (item != (int)blockIdx.x && !*reinterpret_cast<volatile int*>(&sh->abort)) row_epilogue(item - gridDim.x, buf ^ 1);
         return;
     }
     const int c8 = lane & 7, rsub = lane >> 3;
     const int cl = warp * 64 + c8 * 8;          // this lane's first column inside the tile
     const u64 magic = splat(ROUND_MAGIC);
     int q = 0;            // position of the next band to consume in this CTA's band stream
-    int buf = 0;
-    bool aborted = false;
-#ifdef CAME_WIDE_PROFILE
-    long long prof_issue = 0, prof_wait = 0, prof_bar = 0;
-    const long long prof_start = clock64();
-#endif
+    int n = 0;            // items this CTA has gone through
 
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, buf ^= 1) {
-        {
-            // Item barrier: every warp has finished the previous item and the helper has prepared this one.  A warp
-            // that gave up a wait still comes here once per item (see below), so this hardware barrier cannot hang.
-#ifdef CAME_WIDE_PROFILE
-            const long long tb = clock64();
-#endif
-            named_sync(1, ITEM_SYNC);
-#ifdef CAME_WIDE_PROFILE
-            prof_bar += clock64() - tb;
-#endif
-            if (aborted || *reinterpret_cast<volatile int*>(&sh->abort)) { aborted = true; continue; }
-        }
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
+        const int buf = n & 1;
+        if (!wide_wait(&sh->ready[buf], (n >> 1) & 1, sh, a, lane)) return;
         const MomentItem& mi = s_item[buf];
         const int R = mi.R, C = mi.C, row0 = mi.row0, nbands = mi.nbands;
         const bool active = cl < mi.wcols;        // warps beyond a ragged tile width idle
@@ -379,19 +375,11 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
         float a_next = (active && !FLAT) ? amax_dst[0] : 0.0f;
         const float* sr_k = sr + rsub;                                                         // row factors of the band
         float* srow_k = srow + warp * W_TR + rsub;
-        bool ok = true;
 
 #pragma unroll 1
         for (int k = 0; k < nbands; ++k, ++q) {
             const int slot = q % STAGES;
-#ifdef CAME_WIDE_PROFILE
-            const long long t0 = clock64(), t1 = t0;
-#endif
-            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) { ok = false; break; }
-#ifdef CAME_WIDE_PROFILE
-            const long long t2 = clock64();
-            prof_issue += t1 - t0; prof_wait += t2 - t1;
-#endif
+            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) return;      // the status word is set
             if (!active) { wide_release(sh, slot, lane); continue; }
             const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(TG);
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
@@ -502,7 +490,6 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
             }
             mdst += band_bytes; amax_dst += tile_cols; sr_k += W_BAND; srow_k += W_BAND;
         }
-        if (!ok) { aborted = true; continue; }
         // column partials: the 4 row groups of a warp hold partial sums of the same 8 columns
         if (active) {
 #pragma unroll
@@ -514,15 +501,10 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
                 if (rsub == 0) *reinterpret_cast<float2*>(mi.colpart + (int64_t)mi.tr * C + col + 2 * j) = make_float2(lo, hi);
             }
         }
+        // this warp is through with the item: its row partials are in shared memory for the helper warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->done[buf]);
     }
-#ifdef CAME_WIDE_PROFILE
-    if ((blockIdx.x == 0 || blockIdx.x == 77) && lane == 0 && (warp == 0 || warp == 5 || warp == 15))
-        printf("moment cta %d warp %d: total %lld issue %lld wait_full %lld item_barrier %lld bands %d\n", blockIdx.x, warp,
-               clock64() - prof_start, prof_issue, prof_wait, prof_bar, q);
-#endif
-    // after this barrier the last item's row partials are complete (the helper warp sums them)
-    named_sync(1, ITEM_SYNC);
-    if ((aborted || *reinterpret_cast<volatile int*>(&sh->abort)) && warp == 0) wide_drain(sh, STAGES);
 }
 
 // ------------------------------------------------------------------------------------------------
