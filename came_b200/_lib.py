@@ -72,6 +72,7 @@ SYMBOLS = {
     "came_b200_plan_set_pointers": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
                                                C.c_void_p]),
     "came_b200_step": (C.c_int, [C.c_void_p, C.POINTER(CameHyper), C.c_int, C.c_void_p]),
+    "came_b200_plan_set_hyper": (C.c_int, [C.c_void_p, C.POINTER(CameHyper), C.c_int]),
     "came_b200_plan_last_launches": (C.c_int, [C.c_void_p]),
     "came_b200_plan_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "came_b200_plan_set_timing": (C.c_int, [C.c_void_p, C.c_int]),

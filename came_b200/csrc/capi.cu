@@ -121,9 +121,9 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.scal = take(4);
         s.rowpart = take((size_t)std::max(g.tiles_c, g.ptiles_c) * (size_t)g.R);
         s.sq_col_parts = g.tiles_r;
-        int fa_groups = 1, fa_ng = 1, fa_rb = 1, fa_stages = 3;
+        int fa_groups = 1, fa_ng = 1, fa_rb = 1;
         if (vec_flags(d).k == 2) {
-            fused_sq_geometry(g.C, elem_bytes(d.g_dtype), &fa_groups, &fa_ng, &fa_rb, &fa_stages);
+            fused_sq_geometry(g.C, elem_bytes(d.g_dtype), &fa_groups, &fa_ng, &fa_rb);
             s.sq_col_parts = g.tiles_r * fa_groups;
         }
         s.colpart = take((size_t)std::max(s.sq_col_parts, g.ptiles_r) * (size_t)g.C);
@@ -136,7 +136,6 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
             s.fa_rb = fa_rb;
-            s.fa_stages = fa_stages;
             s.tpart = take((size_t)s.sq_col_parts * (size_t)g.C);
         }
     }
@@ -224,10 +223,37 @@ struct came_plan {
     bool timing = false;
     struct Timed { int kernel; cudaEvent_t t0, t1; };
     std::vector<Timed> timed;
+    // page-locked copy of the hyper-parameter records: the source of the upload when a step is captured into a
+    // CUDA graph (the graph's copy node reads it again at every replay)
+    CameHyper* graph_hyp = nullptr;
+    int graph_groups = 0;
     ~came_plan() {
         for (auto& t : timed) { cudaEventDestroy(t.t0); cudaEventDestroy(t.t1); }
+        if (graph_hyp) cudaFreeHost(graph_hyp);
     }
 };
+
+static int check_hypers(const char* who, const came_plan* plan, const CameHyper* hypers, int n_groups) {
+    if (!plan || !hypers) return fail(CAME_E_INVALID, "%s: null argument", who);
+    if (n_groups <= 0 || n_groups > MAX_GROUPS) return fail(CAME_E_INVALID, "%s: n_groups %d outside [1, %d]", who, n_groups, MAX_GROUPS);
+    for (const auto& d : plan->descs)
+        if (d.group >= n_groups) return fail(CAME_E_INVALID, "%s: a tensor refers to group %d, %d given", who, d.group, n_groups);
+    for (int i = 0; i < n_groups; ++i) {
+        if (!(hypers[i].clip_threshold > 0.0f)) return fail(CAME_E_INVALID, "%s: group %d: clip_threshold must be > 0", who, i);
+    }
+    return CAME_OK;
+}
+
+static int stage_graph_hypers(const char* who, came_plan* plan, const CameHyper* hypers, int n_groups) {
+    if (!plan->graph_hyp) {
+        const cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&plan->graph_hyp), (size_t)MAX_GROUPS * sizeof(CameHyper),
+                                            cudaHostAllocDefault);
+        if (e != cudaSuccess) { plan->graph_hyp = nullptr; return fail(CAME_E_CUDA, "%s: cudaHostAlloc: %s", who, cudaGetErrorString(e)); }
+    }
+    std::memcpy(plan->graph_hyp, hypers, (size_t)n_groups * sizeof(CameHyper));
+    plan->graph_groups = n_groups;
+    return CAME_OK;
+}
 
 extern "C" {
 
@@ -331,21 +357,13 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
     auto fusedA = [&](int i) { return D[i].cols != 0 && vf[i].k == 2; };
     auto twopass = [&](int i) { return D[i].cols != 0 && vf[i].k != 2; };
-    auto fused_code = [&](int i) {      // column groups per thread | warp groups << 4
-        int groups, ng, rb, stages;
-        fused_sq_geometry(D[i].cols, elem_bytes(D[i].g_dtype), &groups, &ng, &rb, &stages);
+    auto fused_code = [&](int i) {      // column groups per thread | row sets << 4
+        int groups, ng, rb;
+        fused_sq_geometry(D[i].cols, elem_bytes(D[i].g_dtype), &groups, &ng, &rb);
         return ng | (groups << 4);
     };
     build(KID_SQ_PARTIALS, fusedA, [&](int i) { return Key{D[i].g_dtype, 0, fused_code(i), 2}; },
           [&](int i) { return (int64_t)geo[i].tiles_r; });
-    for (auto& it : plan->launches)   // shared memory of each fused launch = the largest ring among its tensors
-        if (it.kernel == KID_SQ_PARTIALS)
-            for (int i = 0; i < n_tensors; ++i)
-                if (fusedA(i) && D[i].g_dtype == it.key.g_dtype && fused_code(i) == it.key.mode)
-                    it.extra = std::max(it.extra, (size_t)scr[i].fa_stages * (size_t)scr[i].fa_rb * (size_t)D[i].cols *
-                                                      elem_bytes(D[i].g_dtype));
-    build(KID_SQ_PARTIALS, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
-          [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
     build(KID_SUMSQ, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
@@ -410,18 +428,33 @@ int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* c
     return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "set_pointers: %s", cudaGetErrorString(e));
 }
 
+int came_b200_plan_set_hyper(came_plan_t* plan, const CameHyper* hypers, int n_groups) {
+    int rc = check_hypers("plan_set_hyper", plan, hypers, n_groups);
+    if (rc != CAME_OK) return rc;
+    if (plan->graph_hyp && n_groups != plan->graph_groups)
+        return fail(CAME_E_INVALID, "plan_set_hyper: %d groups given, the captured step has %d", n_groups, plan->graph_groups);
+    return stage_graph_hypers("plan_set_hyper", plan, hypers, n_groups);
+}
+
 int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, came_stream_t stream) {
-    if (!plan || !hypers) return fail(CAME_E_INVALID, "step: null argument");
-    if (n_groups <= 0 || n_groups > MAX_GROUPS) return fail(CAME_E_INVALID, "step: n_groups %d outside [1, %d]", n_groups, MAX_GROUPS);
-    for (const auto& d : plan->descs)
-        if (d.group >= n_groups) return fail(CAME_E_INVALID, "step: a tensor refers to group %d, %d given", d.group, n_groups);
-    for (int i = 0; i < n_groups; ++i) {
-        if (!(hypers[i].clip_threshold > 0.0f)) return fail(CAME_E_INVALID, "step: group %d: clip_threshold must be > 0", i);
-    }
+    int rc = check_hypers("step", plan, hypers, n_groups);
+    if (rc != CAME_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemcpyAsync(plan->ws + plan->L.off_hyp, hypers, (size_t)n_groups * sizeof(CameHyper),
+    // While the stream is being captured into a CUDA graph the upload must read memory that outlives the call:
+    // the plan's page-locked copy, which came_b200_plan_set_hyper rewrites between replays.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) { cap = cudaStreamCaptureStatusNone; cudaGetLastError(); }
+    const bool capturing = cap == cudaStreamCaptureStatusActive;
+    const CameHyper* src = hypers;
+    if (capturing) {
+        rc = stage_graph_hypers("step", plan, hypers, n_groups);
+        if (rc != CAME_OK) return rc;
+        src = plan->graph_hyp;
+    }
+    cudaError_t e = cudaMemcpyAsync(plan->ws + plan->L.off_hyp, src, (size_t)n_groups * sizeof(CameHyper),
                                     cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: hyper-parameter upload: %s", cudaGetErrorString(e));
+    const bool timing = plan->timing && !capturing;      // events are not recorded into a graph
     StepArgs a{reinterpret_cast<const CameTensorDesc*>(plan->ws + plan->L.off_descs),
                reinterpret_cast<const Scratch*>(plan->ws + plan->L.off_scr),
                reinterpret_cast<const CameHyper*>(plan->ws + plan->L.off_hyp),
@@ -430,7 +463,7 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     int launches = 0;
     for (const LaunchItem& it : plan->launches) {
         came_plan::Timed tm{it.kernel, nullptr, nullptr};
-        if (plan->timing) {
+        if (timing) {
             if (cudaEventCreate(&tm.t0) != cudaSuccess || cudaEventCreate(&tm.t1) != cudaSuccess)
                 return fail(CAME_E_CUDA, "step: cudaEventCreate failed");
             cudaEventRecord(tm.t0, st);
@@ -438,10 +471,10 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
         if (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY)
             e = launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         else if (it.kernel == KID_SQ_PARTIALS && it.key.variant == 2)
-            e = launch_fused_sq(it.key, a, wbase + it.work_off, it.n, it.extra, st);
+            e = launch_fused_sq(it.key, a, wbase + it.work_off, it.n, st);
         else
             e = launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
-        if (plan->timing) {
+        if (timing) {
             cudaEventRecord(tm.t1, st);
             plan->timed.push_back(tm);
         }

@@ -49,7 +49,6 @@ struct Scratch {
     int32_t nbR, nbC;             // ceil(rows/256), ceil(cols/256)
     int32_t fused_a;              // 1: the fused first pass runs (complete row sums, v_row and tpart come from it)
     int32_t fa_rb;                // fused first pass: rows per staged batch
-    int32_t fa_stages;            // fused first pass: ring slots
     float* mfac;                  // staged momentum pass: row factors / clip [R], then column factors [C]
     int32_t sq_col_parts;         // column partial sets the first pass leaves (strips, or strips x 2 warp groups)
     int32_t res_eps_deferred;     // 1: the residual partials hold sums of (u-m)^2 only; eps1 is added per row / column

@@ -138,6 +138,11 @@ class DevicePlan:
             stream = torch.cuda.current_stream(self.device).cuda_stream
             _lib.check(self.lib.came_b200_step(self.handle, arr, len(hypers), stream))
 
+    def set_hyper(self, hypers: list) -> None:
+        """Rewrites the hyper-parameter records a captured step uploads at every replay (no stream work)."""
+        arr = (CameHyper * len(hypers))(*hypers)
+        _lib.check(self.lib.came_b200_plan_set_hyper(self.handle, arr, len(hypers)))
+
     @property
     def last_launches(self) -> int:
         return self.lib.came_b200_plan_last_launches(self.handle)
@@ -202,6 +207,10 @@ class StepEngine:
         for dev in [d for d in self.plans if d not in by_dev]:
             self.plans.pop(dev).close()
         return ready
+
+    def set_hyper(self, hypers: list) -> None:
+        for plan in self.plans.values():
+            plan.set_hyper(hypers)
 
     def step(self, entries: list, hypers: list) -> int:
         launches = 0

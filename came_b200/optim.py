@@ -286,6 +286,19 @@ class _CameB200Optimizer(torch.optim.Optimizer):
         if entries:
             self._engine.prepare(entries)
 
+    def update_captured_hypers(self) -> None:
+        """After `step()` has been captured into a CUDA graph: re-reads lr / betas / eps / clip_threshold /
+        weight_decay from `param_groups` and rewrites the records the captured step uploads at each replay, so a
+        learning-rate schedule needs no re-capture.  (The reference's captured kernels carry these values as
+        launch arguments and have to be captured again, CAME8bit2D.py:52-72.)  Call it before launching the
+        replay that should see the new values."""
+        hypers = []
+        for group in self.param_groups:
+            hp = (group["lr"], group["betas"], group["eps"], group["clip_threshold"], group["weight_decay"])
+            hypers.append(make_hyper(*hp, python_scalars=False))
+            hypers.append(make_hyper(*hp, python_scalars=True))
+        self._engine.set_hyper(hypers)
+
     # -- checkpointing --------------------------------------------------------------------------
     def state_dict(self):
         return super().state_dict()

@@ -151,6 +151,18 @@ int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* c
 int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, came_stream_t stream);
 
 /*
+ * CUDA-graph capture.  came_b200_step may be called while `stream` is being captured: nothing in it synchronises
+ * or allocates device memory, and the hyper-parameter upload then reads a page-locked copy kept inside the plan
+ * instead of `hypers`, so the captured copy node stays valid after the call.  Between replays,
+ * came_b200_plan_set_hyper rewrites that copy (learning-rate schedules without re-capturing); it makes no CUDA
+ * call that touches a stream.  The copy node reads the buffer when the graph runs, so rewrite it only when no
+ * replay that should still see the old values is pending.  The gradient and parameter addresses are those of
+ * the plan at capture time.  The reference bakes the learning rate into the captured kernel arguments
+ * (came_pytorch/CAME8bit2D.py:52-72 prime_for_cuda_graph, came_pytorch/CAME8bit.py:672-693).
+ */
+int came_b200_plan_set_hyper(came_plan_t* plan, const CameHyper* hypers, int n_groups);
+
+/*
  * Waits for `stream` and reads the plan's device status word: 0, or 1 when a kernel gave up waiting for a
  * staged copy (every wait inside the kernels is bounded; the step's results are then incomplete).  The
  * reference has no counterpart: it checks no launch or device error at all (no cudaGetLastError in
