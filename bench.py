@@ -54,6 +54,16 @@ def llama7b_shapes():
     return shapes
 
 
+def llama7b_linear_shapes():
+    """The same model with the MLP matrices stored as torch.nn.Linear stores them ([out, in]): gate/up 11008x4096,
+    down 4096x11008 (row and column reductions swap cost)."""
+    shapes = [(32000, 4096)]
+    for _ in range(32):
+        shapes += [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)] + [(4096,)] * 2
+    shapes += [(4096,), (32000, 4096)]
+    return shapes
+
+
 def profile_shapes():
     """A small case of the same kernels for profiler captures: a few matrices of the Llama-7B shapes
     (0.24 G elements, 2 GB on the device; gradients alone are 4x the L2)."""
@@ -98,6 +108,7 @@ def llama3_8b_shapes():
 # name -> (shapes, optimizer class, parameter / gradient dtype, betas)
 WORKLOADS = {
     "llama7b": (llama7b_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
+    "llama7b_linear": (llama7b_linear_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
     "profile": (profile_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
     "gpt2m_camecuda": (gpt2_medium_shapes, "CAMECUDA", "float32", (0.9, 0.999, 0.9999)),
     "llama1b_memory": (llama1b_shapes, "CAME8bitMemory", "bfloat16", (0.9, 0.999, 0.9999)),

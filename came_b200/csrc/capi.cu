@@ -244,12 +244,9 @@ static int check_hypers(const char* who, const came_plan* plan, const CameHyper*
     return CAME_OK;
 }
 
+// (the buffer is allocated when the plan is created: page-locking memory is not allowed while a stream is captured)
 static int stage_graph_hypers(const char* who, came_plan* plan, const CameHyper* hypers, int n_groups) {
-    if (!plan->graph_hyp) {
-        const cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&plan->graph_hyp), (size_t)MAX_GROUPS * sizeof(CameHyper),
-                                            cudaHostAllocDefault);
-        if (e != cudaSuccess) { plan->graph_hyp = nullptr; return fail(CAME_E_CUDA, "%s: cudaHostAlloc: %s", who, cudaGetErrorString(e)); }
-    }
+    if (!plan->graph_hyp) return fail(CAME_E_CUDA, "%s: the plan has no page-locked hyper-parameter buffer", who);
     std::memcpy(plan->graph_hyp, hypers, (size_t)n_groups * sizeof(CameHyper));
     plan->graph_groups = n_groups;
     return CAME_OK;
@@ -364,6 +361,8 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     };
     build(KID_SQ_PARTIALS, fusedA, [&](int i) { return Key{D[i].g_dtype, 0, fused_code(i), 2}; },
           [&](int i) { return (int64_t)geo[i].tiles_r; });
+    build(KID_SQ_PARTIALS, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
+          [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
     build(KID_SUMSQ, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
@@ -400,6 +399,8 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
         e = cudaMemcpyAsync(plan->ws + L.off_work, work.data(), work.size() * sizeof(Work), cudaMemcpyHostToDevice, st);
     // the host vectors above die at return: wait for the copies
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess)
+        e = cudaHostAlloc(reinterpret_cast<void**>(&plan->graph_hyp), (size_t)MAX_GROUPS * sizeof(CameHyper), cudaHostAllocDefault);
     if (e != cudaSuccess) {
         delete plan;
         return fail(CAME_E_CUDA, "plan_create: %s", cudaGetErrorString(e));
@@ -431,7 +432,7 @@ int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* c
 int came_b200_plan_set_hyper(came_plan_t* plan, const CameHyper* hypers, int n_groups) {
     int rc = check_hypers("plan_set_hyper", plan, hypers, n_groups);
     if (rc != CAME_OK) return rc;
-    if (plan->graph_hyp && n_groups != plan->graph_groups)
+    if (plan->graph_groups && n_groups != plan->graph_groups)
         return fail(CAME_E_INVALID, "plan_set_hyper: %d groups given, the captured step has %d", n_groups, plan->graph_groups);
     return stage_graph_hypers("plan_set_hyper", plan, hypers, n_groups);
 }
