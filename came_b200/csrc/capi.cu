@@ -121,9 +121,9 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.scal = take(4);
         s.rowpart = take((size_t)std::max(g.tiles_c, g.ptiles_c) * (size_t)g.R);
         s.sq_col_parts = g.tiles_r;
-        int fa_groups = 1, fa_ng = 1, fa_rb = 1;
+        int fa_groups = 1, fa_ng = 1, fa_rb = 1, fa_slot_kb = 64;
         if (vec_flags(d).k == 2) {
-            fused_sq_geometry(g.C, elem_bytes(d.g_dtype), &fa_groups, &fa_ng, &fa_rb);
+            fused_sq_geometry(g.C, elem_bytes(d.g_dtype), &fa_groups, &fa_ng, &fa_rb, &fa_slot_kb);
             s.sq_col_parts = g.tiles_r * fa_groups;
         }
         s.colpart = take((size_t)std::max(s.sq_col_parts, g.ptiles_r) * (size_t)g.C);
@@ -354,10 +354,10 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
     auto fusedA = [&](int i) { return D[i].cols != 0 && vf[i].k == 2; };
     auto twopass = [&](int i) { return D[i].cols != 0 && vf[i].k != 2; };
-    auto fused_code = [&](int i) {      // column groups per thread | row sets << 4
-        int groups, ng, rb;
-        fused_sq_geometry(D[i].cols, elem_bytes(D[i].g_dtype), &groups, &ng, &rb);
-        return ng | (groups << 4);
+    auto fused_code = [&](int i) {      // column groups per thread | row sets << 4 | ring slot KB << 8
+        int groups, ng, rb, slot_kb;
+        fused_sq_geometry(D[i].cols, elem_bytes(D[i].g_dtype), &groups, &ng, &rb, &slot_kb);
+        return ng | (groups << 4) | (slot_kb << 8);
     };
     build(KID_SQ_PARTIALS, fusedA, [&](int i) { return Key{D[i].g_dtype, 0, fused_code(i), 2}; },
           [&](int i) { return (int64_t)geo[i].tiles_r; });

@@ -102,9 +102,44 @@ __global__ void __launch_bounds__(THREADS) k_sq_partials(StepArgs a, const Work*
 // RES=false: second moment (beta2, partials of pass 1); RES=true: residual (beta3, partials of moment).
 // (reference: came_kernels.cu:77-93, 215-242, 298-333, 2685-2706, 2742-2779, 524-593, 1436-1487)
 // ------------------------------------------------------------------------------------------
+// Sum of the `parts` rows of a [parts x n] matrix of column partials for the 256 columns of block b; the result
+// for column b * 256 + threadIdx.x.  Warp w adds the rows w, w + 8, ... (a lane holds 8 columns: two 16-byte loads
+// per row), then the eight per-warp sums are added in a fixed order: the chain of dependent loads is parts / 8
+// long instead of parts, and the order of the additions does not depend on timing.
+__device__ __forceinline__ float column_partial_sum(const float* __restrict__ part, int parts, int n, int b,
+                                                    float (*s_acc)[QBLOCK]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c0 = b * QBLOCK + lane * 8;
+    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const bool vec = (n & 3) == 0 && (reinterpret_cast<uintptr_t>(part) & 15) == 0 && c0 + 8 <= n;
+    if (vec) {
+#pragma unroll 4
+        for (int t = warp; t < parts; t += THREADS / 32) {
+            const float4* p = reinterpret_cast<const float4*>(part + (int64_t)t * n + c0);
+            const float4 x = p[0], y = p[1];
+            acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+            acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+        }
+    } else {
+        for (int t = warp; t < parts; t += THREADS / 32)
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (c0 + e < n) acc[e] += part[(int64_t)t * n + c0 + e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_acc[warp][lane * 8 + e] = acc[e];
+    __syncthreads();
+    float r = 0.0f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) r += s_acc[w][threadIdx.x];
+    __syncthreads();      // the buffer may be reused right away
+    return r;
+}
+
 template <bool RES>
 __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work* __restrict__ work) {
     __shared__ float red[33];
+    __shared__ float s_acc[THREADS / 32][QBLOCK];
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
     const Scratch& s = a.scr[w.tensor];
@@ -126,6 +161,13 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
     // the fused first pass delivers finished v_row values, column sums without eps0, and tpart
     const bool fused = !RES && s.fused_a;
     float v = 0.0f, tsum = 0.0f;
+    // column partials: summed by the whole block together (every thread takes part, also beyond the last column)
+    float colsum = 0.0f;
+    if (is_col) {
+        const int parts = RES ? s.ptiles_r : s.sq_col_parts;
+        colsum = column_partial_sum(s.colpart, parts, C, b, s_acc);
+        if (fused) tsum = column_partial_sum(s.tpart, parts, C, b, s_acc);
+    }
     if (valid) {
         if (fused && !is_col) {
             v = s.vr[idx];
@@ -137,12 +179,8 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
                 if (RES && s.res_eps_deferred) acc += (float)C * h.eps1;
                 acc = acc / (float)C;
             } else {
-                const int parts = RES ? s.ptiles_r : s.sq_col_parts;
-                for (int t = 0; t < parts; ++t) acc += s.colpart[(int64_t)t * C + idx];
-                if (fused) {
-                    acc += (float)R * h.eps0;
-                    for (int t = 0; t < parts; ++t) tsum += s.tpart[(int64_t)t * C + idx];
-                }
+                acc = colsum;
+                if (fused) acc += (float)R * h.eps0;
                 if (RES && s.res_eps_deferred) acc += (float)R * h.eps1;
                 acc = acc / (float)R;
             }

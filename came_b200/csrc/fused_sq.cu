@@ -7,7 +7,7 @@
 // which holds because r_i^2 = mean(v_row) / v_row_i and c_j^2 = 1 / v_col_j when no 1e-30 clamp is active
 // (tensors carrying CAME_F_SQ_CLAMP take the two-pass kernels instead).  v_row_i needs the complete row,
 // so the unit of work is a strip of 128 whole rows, staged through shared memory in batches of `rb` rows by
-// bulk asynchronous copies into a ring of three 64 KB slots and swept twice from shared memory.
+// bulk asynchronous copies into a 192 KB ring of slots and swept twice from shared memory.
 //
 // Replaces kUpdateSqRowQuantized, the column walk of kUpdateSqColQuantizedFinalize and kSumUpdateSq
 // (came_kernels.cu:61-96, 198-243, 596-619), which read g three times.
@@ -46,8 +46,8 @@ __device__ __forceinline__ void smem_run8(const float* p, u64* out) {
     out[0] = pk(a.x, a.y); out[1] = pk(a.z, a.w); out[2] = pk(b.x, b.y); out[3] = pk(b.z, b.w);
 }
 
-constexpr int FA_SLOTS = 3;                       // ring slots
-constexpr int FA_SLOT_BYTES = 64 * 1024;          // a batch (rb rows) never exceeds this
+constexpr int FA_MAX_SLOTS = 8;
+constexpr int FA_RING_BYTES = 192 * 1024;         // ring = slots x slot bytes; a batch (rb rows) fits one slot
 constexpr int FA_ALL_THREADS = FA_THREADS + 64;   // 16 computing warps, the copy-issuing warp, the row-finalize warp
 constexpr int FA_SYNC = FA_THREADS + 32;          // the computing warps and the row-finalize warp
 
@@ -67,8 +67,8 @@ struct FaStrip {
 // row-finalize warp are through with it.  `wready` = the row weights 1 / v_row of a batch are in shared memory
 // (two buffers, alternating by batch).
 struct FaShared {
-    uint64_t full[FA_SLOTS];
-    uint64_t empty[FA_SLOTS];
+    uint64_t full[FA_MAX_SLOTS];
+    uint64_t empty[FA_MAX_SLOTS];
     uint64_t ready[2];
     uint64_t done[2];
     uint64_t wready[2];
@@ -115,9 +115,10 @@ __device__ __forceinline__ int fa_batches_of(const StepArgs& a, const Work* work
 // After a failed wait a warp keeps walking its batches without touching data, so that it still meets the others at
 // the hardware barrier once per batch (nobody is left waiting).
 template <typename TG, int NG, int RS>
-__global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work, int n_items) {
+__global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work, int n_items,
+                                                                    int n_slots, int slot_bytes) {
     extern __shared__ __align__(128) unsigned char smem[];
-    FaShared* sh = reinterpret_cast<FaShared*>(smem + FA_SLOTS * FA_SLOT_BYTES);
+    FaShared* sh = reinterpret_cast<FaShared*>(smem + FA_RING_BYTES);
     float* s_part = reinterpret_cast<float*>(sh + 1);                // [2][FA_WARPS] row-piece sums, alternating by batch
     float* s_w = s_part + 2 * FA_WARPS;                              // [2][FA_RB]    1 / v_row of a batch's rows
     float* s_old = s_w + 2 * FA_RB;                                  // [2][K_TR]     dequantised old v_row of a strip's rows
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < FA_SLOTS; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], FA_WARPS); }
+        for (int i = 0; i < n_slots; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], FA_WARPS); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->ready[i], 1);
             mbar_init(&sh->done[i], FA_WARPS + 1);
@@ -169,18 +170,18 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
             const uint32_t row_bytes = (uint32_t)C * (uint32_t)sizeof(TG);
             const unsigned char* g_src = reinterpret_cast<const unsigned char*>(d.g) + (int64_t)row0 * row_bytes;
             for (int b = 0; b < nbatch; ++b, ++issued, ++slot) {
-                if (slot == FA_SLOTS) { slot = 0; phase ^= 1u; }
-                if (issued >= FA_SLOTS && !fa_wait(&sh->empty[slot], phase, sh, a, lane)) { ok = false; break; }
+                if (slot == n_slots) { slot = 0; phase ^= 1u; }
+                if (issued >= n_slots && !fa_wait(&sh->empty[slot], phase, sh, a, lane)) { ok = false; break; }
                 const int rows = min(rb, nrows - b * rb);
                 if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * row_bytes);
                 __syncwarp();
                 if (lane < rows)
-                    bulk_g2s(smem + slot * FA_SLOT_BYTES + lane * row_bytes, g_src + (int64_t)(b * rb + lane) * row_bytes,
+                    bulk_g2s(smem + slot * slot_bytes + lane * row_bytes, g_src + (int64_t)(b * rb + lane) * row_bytes,
                              row_bytes, &sh->full[slot]);
             }
         }
         if (!ok) {      // let the copies in flight land before the CTA's shared memory is released
-            for (int i = 0; i < FA_SLOTS; ++i)
+            for (int i = 0; i < n_slots; ++i)
                 for (uint32_t t = 0; t < (1u << 16); ++t)
                     if (mbar_try_wait(&sh->full[i], 0) || mbar_try_wait(&sh->full[i], 1)) break;
         }
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
             const int rows = min(rb, nrows - b * rb);
             float acc_t = 0.0f;
             if (my_row < rows) {
-                const TG* src = reinterpret_cast<const TG*>(smem + sl * FA_SLOT_BYTES + my_row * row_bytes);
+                const TG* src = reinterpret_cast<const TG*>(smem + sl * slot_bytes + my_row * row_bytes);
                 u64 acc[4] = {F2ZERO, F2ZERO, F2ZERO, F2ZERO};
                 // whole 32-group chunks without a per-lane test, then the ragged end of the piece
                 const TG* p = src + (cg_lo + lane) * 8;
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
         };
         auto col_sweep = [&](int b, int sl, const float* wv) {
             const int rows = min(rb, nrows - b * rb);
-            const TG* src = reinterpret_cast<const TG*>(smem + sl * FA_SLOT_BYTES + rset * row_bytes);
+            const TG* src = reinterpret_cast<const TG*>(smem + sl * slot_bytes + rset * row_bytes);
 #pragma unroll 2
             for (int r = rset; r < rows; r += RS, src += RS * C) {
                 const u64 w2 = splat(wv[r]);
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
         for (int b = 0; b < nbatch; ++b, ++gb) {
             int nslot = slot + 1;
             uint32_t nphase = phase;
-            if (nslot == FA_SLOTS) { nslot = 0; nphase ^= 1u; }
+            if (nslot == n_slots) { nslot = 0; nphase ^= 1u; }
             if (ok && b + 1 < nbatch) {
                 if (fa_wait(&sh->full[nslot], nphase, sh, a, lane)) row_sweep(b + 1, nslot, s_part + ((gb + 1) & 1) * FA_WARPS);
                 else ok = false;
@@ -350,16 +351,22 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
 // Geometry of the fused first pass for a matrix of `cols` columns of `elem_bytes` each:
 //   groups   row sets of the column sweep: 2 up to 2048 columns, else 1
 //   ng       8-column groups per thread in the column sweep (1..4)
-//   rb       rows per staged batch: the largest power of two that fits a 64 KB ring slot, between 1 and 16 (the
-//            cost of a batch is mostly fixed, so large batches pay)
-void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb) {
+//   slot_kb  ring slot size in KB (the 192 KB ring holds 192 / slot_kb slots; all tensors of a launch share it)
+//   rb       rows per staged batch: the largest power of two that fits a slot, between 1 and 16 (the cost of a
+//            batch is mostly fixed, so large batches pay)
+void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb, int* slot_kb) {
     const int64_t ncg = cols / 8;
     const int g = ncg <= FA_THREADS / 2 ? 2 : 1;
     const int n = g == 2 ? 1 : (int)((ncg + FA_THREADS - 1) / FA_THREADS);
     const int64_t row_bytes = cols * elem_bytes;
+    int kb = 64;
+#ifdef CAME_TUNE      // build-time experiment switch: geometry overrides from the environment
+    if (const char* e = getenv(n >= 3 ? "CAME_FA_SLOT_KB_WIDE" : "CAME_FA_SLOT_KB")) kb = atoi(e);
+    if (row_bytes > (int64_t)kb * 1024) kb = 64;
+#endif
     int64_t r = 1;
-    while (r < FA_RB && 2 * r * row_bytes <= FA_SLOT_BYTES) r *= 2;
-    *groups = g; *ng = n < 1 ? 1 : n; *rb = (int)r;
+    while (r < FA_RB && 2 * r * row_bytes <= (int64_t)kb * 1024) r *= 2;
+    *groups = g; *ng = n < 1 ? 1 : n; *rb = (int)r; *slot_kb = kb;
 }
 
 bool fused_sq_eligible(int64_t cols, int elem_bytes) {
@@ -367,7 +374,7 @@ bool fused_sq_eligible(int64_t cols, int elem_bytes) {
 }
 
 template <typename TG, int NG, int RS>
-static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, cudaStream_t st) {
+static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, int slot_kb, cudaStream_t st) {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -375,33 +382,36 @@ static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, cudaSt
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    const size_t smem = (size_t)FA_SLOTS * FA_SLOT_BYTES + sizeof(FaShared) +
+    const size_t smem = (size_t)FA_RING_BYTES + sizeof(FaShared) +
                         (2 * FA_WARPS + 2 * FA_RB + 2 * K_TR) * sizeof(float) + 2 * sizeof(FaStrip);
     cudaError_t e = cudaFuncSetAttribute(k_sqstat_fused<TG, NG, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    k_sqstat_fused<TG, NG, RS><<<n < sms ? n : sms, FA_ALL_THREADS, smem, st>>>(a, work, n);
+    const int slot_bytes = slot_kb * 1024;
+    int n_slots = FA_RING_BYTES / slot_bytes;
+    if (n_slots > FA_MAX_SLOTS) n_slots = FA_MAX_SLOTS;
+    k_sqstat_fused<TG, NG, RS><<<n < sms ? n : sms, FA_ALL_THREADS, smem, st>>>(a, work, n, n_slots, slot_bytes);
     return cudaGetLastError();
 }
 
 template <typename TG>
-static cudaError_t launch_ng(int ng, int groups, const StepArgs& a, const Work* work, int n, cudaStream_t st) {
-    if (groups == 2) return launch_one<TG, 1, 2>(a, work, n, st);      // at most 2048 columns: one column group per thread
+static cudaError_t launch_ng(int ng, int groups, int slot_kb, const StepArgs& a, const Work* work, int n, cudaStream_t st) {
+    if (groups == 2) return launch_one<TG, 1, 2>(a, work, n, slot_kb, st);      // at most 2048 columns: one column group per thread
     switch (ng) {
-        case 1: return launch_one<TG, 1, 1>(a, work, n, st);
-        case 2: return launch_one<TG, 2, 1>(a, work, n, st);
-        case 3: return launch_one<TG, 3, 1>(a, work, n, st);
-        default: return launch_one<TG, 4, 1>(a, work, n, st);
+        case 1: return launch_one<TG, 1, 1>(a, work, n, slot_kb, st);
+        case 2: return launch_one<TG, 2, 1>(a, work, n, slot_kb, st);
+        case 3: return launch_one<TG, 3, 1>(a, work, n, slot_kb, st);
+        default: return launch_one<TG, 4, 1>(a, work, n, slot_kb, st);
     }
 }
 
-// key.mode carries ng | (groups << 4); all tensors of one launch share it
+// key.mode carries ng | (groups << 4) | (slot KB << 8); all tensors of one launch share it
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
-    const int ng = key.mode & 15, groups = key.mode >> 4;
+    const int ng = key.mode & 15, groups = (key.mode >> 4) & 15, slot_kb = key.mode >> 8;
     switch (key.g_dtype) {
-        case CAME_DT_F32: return launch_ng<float>(ng, groups, a, work, n, st);
-        case CAME_DT_F16: return launch_ng<__half>(ng, groups, a, work, n, st);
-        default: return launch_ng<__nv_bfloat16>(ng, groups, a, work, n, st);
+        case CAME_DT_F32: return launch_ng<float>(ng, groups, slot_kb, a, work, n, st);
+        case CAME_DT_F16: return launch_ng<__half>(ng, groups, slot_kb, a, work, n, st);
+        default: return launch_ng<__nv_bfloat16>(ng, groups, slot_kb, a, work, n, st);
     }
 }
 

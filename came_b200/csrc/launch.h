@@ -45,7 +45,7 @@ cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& 
                               cudaStream_t st);
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, cudaStream_t st);
 constexpr int S_FIN_CHUNK = 2048;      // factor-vector entries one CTA of the clip finalize writes
-void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb);
+void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb, int* slot_kb);
 bool fused_sq_eligible(int64_t cols, int elem_bytes);
 cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                                cudaStream_t st);

@@ -162,6 +162,22 @@ def test_flat_classes(cls_name, f16, dtype, shapes, hyper):
     assert st["exp_avg_sq_row_q"].data_ptr() == st["factored_row_q"][0].data_ptr()
 
 
+# Many work items per persistent CTA: 450 strips / row tiles of 128 rows against 148 CTAs, so every CTA walks
+# several items, its double-buffered item records are reused and its copy ring wraps across item boundaries.
+MANY_ITEM_SHAPES = [(38400, 64), (12800, 256), (6400, 1280), (4096,)]
+
+
+@pytest.mark.parametrize("cls_name,preset2d", [("CAME8bit", "TILE8"), ("CAME8bitFull", "FLAT8")])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_many_items_per_cta(cls_name, preset2d, dtype):
+    import came_b200
+    preset = lambda dim: getattr(orc, preset2d) if dim == 2 else orc.FLAT8
+    out, opt, gp = run_pair(getattr(came_b200, cls_name), preset, MANY_ITEM_SHAPES, _dt(dtype), 2, H_LLAMA, seed=21)
+    _check_8bit(out, _dt(dtype))
+    for plan in opt._engine.plans.values():
+        assert plan.status() == 0
+
+
 def test_mixed_grad_dtype_takes_flat_layout():
     """CAME8bit.py:216-223: a 2-D tensor whose gradient dtype differs from the parameter dtype does not
     take the tile path."""
