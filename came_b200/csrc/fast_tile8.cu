@@ -184,28 +184,33 @@ struct WideProducer {
         live = item < n_items;
         if (live) it = wide_item<TA>(a, work[item], a_is_grad);
     }
-    // issue the next band of the stream (all 32 lanes of warp 0 call this); false on a timed-out wait
+    // Issue the next band of the stream (all 32 lanes of a producer warp call this); false on a timed-out wait.
+    // With `nprod` producer warps, warp `which` copies the bands whose stream position is `which` modulo nprod and
+    // only steps over the others (one warp alone tops out near 5.7 TB/s of copies per GPU, two reach 6.5: measured
+    // on the bare ring).
     __device__ __forceinline__ bool issue(const StepArgs& a, const Work* work, int n_items, bool a_is_grad,
-                                          unsigned char* smem, WideShared* sh, int lane) {
+                                          unsigned char* smem, WideShared* sh, int lane, int which = 0, int nprod = 1) {
         if (!live) return true;
         constexpr int STAGE = WideCfg<TA>::STAGE, ROW = WideCfg<TA>::ROW;
-        const int slot = q % STAGES;
-        if (q >= STAGES) {   // every consumer warp must have released the slot's previous band
-            if (!wide_wait(&sh->empty[slot], ((q / STAGES) - 1) & 1, sh, a, lane)) return false;
-        }
-        const int rows = min(W_BAND, it.R - it.row0 - band * W_BAND);
-        const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(TA), m_bytes = (uint32_t)it.wcols;
-        const uint32_t x_bytes = it.x_src ? (uint32_t)(it.wcols >> 4) * sizeof(float) : 0u;   // a multiple of 16: wcols % 64 == 0
-        if (lane == 0) {
-            mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (a_bytes + m_bytes) + x_bytes);
-            if (x_bytes) bulk_g2s(smem + slot * STAGE + WideCfg<TA>::AMAX_OFF, it.x_src + band * it.x_pitch, x_bytes, &sh->full[slot]);
-        }
-        __syncwarp();
-        const int r = lane & 15;
-        if (r < rows) {
-            const int64_t row = band * W_BAND + r;
-            if (lane < 16) bulk_g2s(smem + slot * STAGE + r * ROW, it.a_src + row * it.a_pitch, a_bytes, &sh->full[slot]);
-            else bulk_g2s(smem + slot * STAGE + W_BAND * ROW + r * W_MROW, it.m_src + row * it.m_pitch, m_bytes, &sh->full[slot]);
+        if (nprod == 1 || q % nprod == which) {
+            const int slot = q % STAGES;
+            if (q >= STAGES) {   // every consumer warp must have released the slot's previous band
+                if (!wide_wait(&sh->empty[slot], ((q / STAGES) - 1) & 1, sh, a, lane)) return false;
+            }
+            const int rows = min(W_BAND, it.R - it.row0 - band * W_BAND);
+            const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(TA), m_bytes = (uint32_t)it.wcols;
+            const uint32_t x_bytes = it.x_src ? (uint32_t)(it.wcols >> 4) * sizeof(float) : 0u;   // a multiple of 16: wcols % 64 == 0
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (a_bytes + m_bytes) + x_bytes);
+                if (x_bytes) bulk_g2s(smem + slot * STAGE + WideCfg<TA>::AMAX_OFF, it.x_src + band * it.x_pitch, x_bytes, &sh->full[slot]);
+            }
+            __syncwarp();
+            const int r = lane & 15;
+            if (r < rows) {
+                const int64_t row = band * W_BAND + r;
+                if (lane < 16) bulk_g2s(smem + slot * STAGE + r * ROW, it.a_src + row * it.a_pitch, a_bytes, &sh->full[slot]);
+                else bulk_g2s(smem + slot * STAGE + W_BAND * ROW + r * W_MROW, it.m_src + row * it.m_pitch, m_bytes, &sh->full[slot]);
+            }
         }
         ++q;
         if (++band == it.nbands) {
@@ -244,6 +249,9 @@ __device__ __forceinline__ float warp_vector_sum(const float* x, int n, int lane
 // What the computing warps need to know about a work item, prepared in shared memory by the helper warp while
 // the previous item is being computed (reading it from the tables in global memory would put a chain of
 // dependent loads at the start of every item, which the computing warps cannot hide).
+constexpr int M_PRODUCERS = 2;                                          // copy-issuing warps of the momentum pass
+constexpr int M_ALL_THREADS = W_THREADS + 32 * (M_PRODUCERS + 1);       // + the helper warp
+
 struct MomentItem {
     int8_t* m;              // codes of the tensor
     float* m_absmax;
@@ -253,7 +261,7 @@ struct MomentItem {
 };
 
 template <typename TG, bool FLAT>
-__global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
+__global__ void __launch_bounds__(M_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs a, const Work* __restrict__ work, int n_items) {
     constexpr int STAGES = WideCfg<TG>::STAGES, STAGE = WideCfg<TG>::STAGE, ROW = WideCfg<TG>::ROW;
     extern __shared__ __align__(128) unsigned char smem[];
     WideShared* sh = reinterpret_cast<WideShared*>(smem + STAGES * STAGE);
@@ -272,15 +280,16 @@ __global__ void __launch_bounds__(W_ALL_THREADS + 32, 1) k_moment_tile8_wide(Ste
     __syncthreads();
     // No CTA-wide barrier from here on: the warps meet only through the ring and the item barriers below, all with
     // bounded, abort-aware waits, so a warp that gives up simply leaves and the others follow at their next wait.
-    if (warp == W_WARPS) {      // producer warp: run the copy stream as far ahead as the ring allows
+    if (warp < W_WARPS + M_PRODUCERS && warp >= W_WARPS) {
+        // producer warps: run the copy stream as far ahead as the ring allows, alternate bands each
         WideProducer<TG> prod;
         prod.init(a, work, n_items, true);
-        while (prod.live && prod.issue(a, work, n_items, true, smem, sh, lane)) {}
+        while (prod.live && prod.issue(a, work, n_items, true, smem, sh, lane, warp - W_WARPS, M_PRODUCERS)) {}
         // after a failed wait somewhere in the CTA: let the copies in flight land before shared memory is released
         if (*reinterpret_cast<volatile int*>(&sh->abort)) wide_drain(sh, STAGES);
         return;
     }
-    if (warp == W_WARPS + 1) {
+    if (warp == W_WARPS + M_PRODUCERS) {
         // Helper warp.  Items alternate between two buffers (factor slices, item record, per-warp row partials).
         // For the n-th item of this CTA the helper waits until every computing warp has finished it (`done`), sums
         // its per-warp row partials in a fixed order, then prepares item n+2 in the same buffer and publishes it
@@ -854,15 +863,15 @@ cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& 
     if (kernel == KID_MOMENT) {
         if (key.mode == CAME_MODE_FLAT8) {
             switch (key.g_dtype) {
-                case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, true>, moment_smem<float>(), a, work, n, st, W_ALL_THREADS + 32);
-                case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, true>, moment_smem<__half>(), a, work, n, st, W_ALL_THREADS + 32);
-                default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, true>, moment_smem<__nv_bfloat16>(), a, work, n, st, W_ALL_THREADS + 32);
+                case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, true>, moment_smem<float>(), a, work, n, st, M_ALL_THREADS);
+                case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, true>, moment_smem<__half>(), a, work, n, st, M_ALL_THREADS);
+                default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, true>, moment_smem<__nv_bfloat16>(), a, work, n, st, M_ALL_THREADS);
             }
         }
         switch (key.g_dtype) {
-            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, false>, moment_smem<float>(), a, work, n, st, W_ALL_THREADS + 32);
-            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, false>, moment_smem<__half>(), a, work, n, st, W_ALL_THREADS + 32);
-            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, false>, moment_smem<__nv_bfloat16>(), a, work, n, st, W_ALL_THREADS + 32);
+            case CAME_DT_F32: return launch_persistent(k_moment_tile8_wide<float, false>, moment_smem<float>(), a, work, n, st, M_ALL_THREADS);
+            case CAME_DT_F16: return launch_persistent(k_moment_tile8_wide<__half, false>, moment_smem<__half>(), a, work, n, st, M_ALL_THREADS);
+            default: return launch_persistent(k_moment_tile8_wide<__nv_bfloat16, false>, moment_smem<__nv_bfloat16>(), a, work, n, st, M_ALL_THREADS);
         }
     }
     if (kernel == KID_APPLY_FLAT) {
