@@ -41,7 +41,7 @@ STEP_BYTES_1D = 2.0 + 4.0 + 2.0 + 2.0 + 16.0 / 256         # g, p r/w, m r/w, v 
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one launch on the
 # small `--workload profile` case, profiles/tile8_kernels_profile_workload.md); traffic grows in proportion to
 # the element count, so a full launch is this figure times the elements it processes
-NCU_TRAFFIC_BYTES_PER_ELEM = {"sq_partials": 2.05, "moment": 3.97, "apply": 4.79}
+NCU_TRAFFIC_BYTES_PER_ELEM = {"sq_partials": 2.05, "moment": 3.95, "apply": 4.80}
 
 
 def llama7b_shapes():
