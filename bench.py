@@ -117,6 +117,19 @@ WORKLOADS = {
 }
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    """Writes the result line to the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -232,7 +245,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -276,7 +289,8 @@ def run_gpu(args):
     for p, i in zip(params, sp.owned):
         p.grad = (torch.randn(p.shape, generator=ggen, device=dev) * scales[i]).to(pdtype)
     by_index = dict(zip(sp.owned, params))
-    stepper = ShardedStepper(sp, by_index, lambda ps: getattr(came_b200, cls_name)(ps, **dict(HYPER, betas=betas)))
+    stepper = ShardedStepper(sp, by_index, lambda ps: getattr(came_b200, cls_name)(ps, **dict(HYPER, betas=betas)),
+                             gather_mode=args.gather)
     owned_elems = sum(numels[i] for i in sp.owned)
     owned_2d = sum(numels[i] for i in sp.owned if len(shapes[i]) == 2)
     owned_1d = owned_elems - owned_2d
@@ -306,7 +320,7 @@ def run_gpu(args):
 
     # separate legs (multi-GPU only): the step without the gather, and the gather alone
     ms_step_only_total = timed(lambda: stepper.step(gather=False), args.steps) if world > 1 else 0.0
-    ms_ag_total = timed(lambda: [w.wait() for w in sp.all_gather(async_op=True)], args.steps) if world > 1 else 0.0
+    ms_ag_total = timed(stepper.gather_only, args.steps) if world > 1 else 0.0
     for plan in plans:
         plan.set_timing(True)
     with ClockSampler(physical_gpu_index(local)) as clocks:
@@ -398,8 +412,8 @@ def run_gpu(args):
             "tensors every step; 54 GB touched per step, far above the 126 MB L2)",
             "config": {"workload": args.workload, "optimizer": cls_name, "param_dtype": dtype_name,
                        "tensors": len(shapes), "elements": total_elems,
-                       "parallelism": f"ownership x{world}, {n_buckets} buckets, all-gather of bucket b overlapped with the "
-                                      f"step of bucket b+1" if world > 1 else "single GPU",
+                       "parallelism": f"ownership x{world}, {n_buckets} buckets, gather of bucket b ({args.gather}) overlapped "
+                                      f"with the step of bucket b+1" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2"},
             "roofline": roofline,
             "step_roofline": {"alg_bytes_per_step_rank0": step_bytes, "achieved": step_gbs, "peak": peak,
@@ -417,13 +431,13 @@ def run_gpu(args):
                 "note": "value / ms_per_step time the overlapped step + all-gather; the two legs below are timed alone",
                 "step_only_ms": ms_step_only, "step_only_gelem_s": total_elems / (ms_step_only * 1e-3) / 1e9,
                 "all_gather_ms": ag_ms, "all_gather_gbs_in": sp.gathered_bytes_per_rank() / (ag_ms * 1e-3) / 1e9,
-                "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world)}
+                "gather": args.gather, "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world)}
         if world == 1 and not args.no_cpu_baseline:
             dt, elems = cpu_step_time(2, 1)
             line["cpu_baseline"] = {"value": elems / dt / 1e9, "unit": "Gelem/s", "cores": torch.get_num_threads(),
                                     "kind": "port", "sample": "one 4096x4096, 4096x11008, 11008x4096 matrix and one "
                                     "4096 vector of the Llama-7B set, 2 timed passes of the CPU restatement"}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -437,10 +451,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buckets", type=int, default=0, help="all-gather buckets at N > 1 (0: 4 when N > 1, else 1)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="exchange of updated weights at N > 1: copy-engine pulls over CUDA IPC mappings, or NCCL all-gather")
     ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
                     help="llama7b: the benchmark workload (BASELINE config 3); profile: a small case of the same kernels "
                          "for ncu; the others are BASELINE configs 2, 4 and 5")
     args = ap.parse_args()
+    # The contract is ONE JSON line on stdout.  Libraries (NCCL's version banner, for one) write to file descriptor
+    # 1 as well, so everything but that line is sent to stderr: fd 1 is pointed at stderr for the run and the line
+    # is written to the saved descriptor.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -73,6 +73,10 @@ SYMBOLS = {
                                                C.c_void_p]),
     "came_b200_step": (C.c_int, [C.c_void_p, C.POINTER(CameHyper), C.c_int, C.c_void_p]),
     "came_b200_plan_set_hyper": (C.c_int, [C.c_void_p, C.POINTER(CameHyper), C.c_int]),
+    "came_b200_peer_copy_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
+    "came_b200_ipc_export": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "came_b200_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "came_b200_ipc_close": (C.c_int, [C.c_void_p]),
     "came_b200_plan_last_launches": (C.c_int, [C.c_void_p]),
     "came_b200_plan_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "came_b200_plan_set_timing": (C.c_int, [C.c_void_p, C.c_int]),

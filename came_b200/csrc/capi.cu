@@ -210,6 +210,21 @@ Layout layout(const CameTensorDesc* descs, int n) {
 namespace came {
 // lets other translation units leave a message for came_b200_last_error()
 void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+int persistent_grid_limit() {
+    static int limit = 0;
+    if (limit == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        int reserved = 0;
+        if (const char* e = getenv("CAME_B200_RESERVED_SMS")) reserved = atoi(e);
+        if (reserved < 0) reserved = 0;
+        if (reserved > sms - 1) reserved = sms - 1;
+        limit = sms - reserved;
+    }
+    return limit;
+}
 }  // namespace came
 
 struct came_plan {
@@ -484,6 +499,56 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     }
     plan->last_launches = launches;
     return CAME_OK;
+}
+
+int came_b200_peer_copy_async(void* dst, const void* src, size_t bytes, int src_device, came_stream_t stream) {
+    if (!dst || !src) return fail(CAME_E_INVALID, "peer_copy_async: null pointer");
+    if (bytes == 0) return CAME_OK;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(CAME_E_CUDA, "peer_copy_async: %s", cudaGetErrorString(e));
+    if (src_device >= 0 && src_device != dev) {
+        e = cudaDeviceEnablePeerAccess(src_device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+        if (e != cudaSuccess) return fail(CAME_E_CUDA, "peer_copy_async: enabling access to GPU %d: %s", src_device, cudaGetErrorString(e));
+    }
+    e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "peer_copy_async: %s", cudaGetErrorString(e));
+}
+
+int came_b200_ipc_export(const void* ptr, unsigned char handle[CAME_B200_IPC_HANDLE_BYTES], uint64_t* offset) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == CAME_B200_IPC_HANDLE_BYTES, "IPC handle size");
+    if (!ptr || !handle || !offset) return fail(CAME_E_INVALID, "ipc_export: null argument");
+    // base of the allocation that contains ptr (driver entry point: the runtime has no such query)
+    typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || !fn) return fail(CAME_E_CUDA, "ipc_export: cuMemGetAddressRange is not available");
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (reinterpret_cast<range_fn>(fn)(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0)
+        return fail(CAME_E_CUDA, "ipc_export: the pointer is not inside a device allocation");
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>((uintptr_t)base));
+    if (e != cudaSuccess) return fail(CAME_E_CUDA, "ipc_export: %s", cudaGetErrorString(e));
+    std::memcpy(handle, &h, sizeof(h));
+    *offset = (uint64_t)((uintptr_t)ptr - (uintptr_t)base);
+    return CAME_OK;
+}
+
+int came_b200_ipc_open(const unsigned char handle[CAME_B200_IPC_HANDLE_BYTES], void** base) {
+    if (!handle || !base) return fail(CAME_E_INVALID, "ipc_open: null argument");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    const cudaError_t e = cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "ipc_open: %s", cudaGetErrorString(e));
+}
+
+int came_b200_ipc_close(void* base) {
+    if (!base) return CAME_OK;
+    const cudaError_t e = cudaIpcCloseMemHandle(base);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "ipc_close: %s", cudaGetErrorString(e));
 }
 
 int came_b200_plan_last_launches(const came_plan_t* plan) { return plan ? plan->last_launches : 0; }

@@ -844,13 +844,7 @@ template <typename T> static constexpr size_t flat_smem() {
 template <typename K>
 static cudaError_t launch_persistent(K kernel, size_t smem, const StepArgs& a, const Work* work, int n, cudaStream_t st,
                                      int threads = W_ALL_THREADS) {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-    }
+    const int sms = persistent_grid_limit();
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kernel<<<n < sms ? n : sms, threads, smem, st>>>(a, work, n);

@@ -375,13 +375,7 @@ bool fused_sq_eligible(int64_t cols, int elem_bytes) {
 
 template <typename TG, int NG, int RS>
 static cudaError_t launch_one(const StepArgs& a, const Work* work, int n, int slot_kb, cudaStream_t st) {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-    }
+    const int sms = persistent_grid_limit();
     const size_t smem = (size_t)FA_RING_BYTES + sizeof(FaShared) +
                         (2 * FA_WARPS + 2 * FA_RB + 2 * K_TR) * sizeof(float) + 2 * sizeof(FaStrip);
     cudaError_t e = cudaFuncSetAttribute(k_sqstat_fused<TG, NG, RS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

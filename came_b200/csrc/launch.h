@@ -44,6 +44,10 @@ cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a,
 cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                               cudaStream_t st);
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, cudaStream_t st);
+// CTAs a persistent kernel launches: the SM count of the current device minus CAME_B200_RESERVED_SMS (environment,
+// read once; default 0).  Leaving a few SMs free lets small kernels of other streams (a collective's flag
+// exchange, say) start while a persistent pass occupies the rest for milliseconds.
+int persistent_grid_limit();
 constexpr int S_FIN_CHUNK = 2048;      // factor-vector entries one CTA of the clip finalize writes
 void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* rb, int* slot_kb);
 bool fused_sq_eligible(int64_t cols, int elem_bytes);

@@ -15,6 +15,8 @@ import math
 import torch
 import torch.distributed as dist
 
+from . import _lib
+
 ALIGN_ELEMS = 128   # every tensor starts on a 256-byte boundary (bf16), keeping the 16-byte vector paths
 
 
@@ -108,17 +110,89 @@ class ShardedParams:
         return (self.world_size - 1) * self.slice_len * self.flat.element_size()
 
 
+class PeerGather:
+    """The all-gather of updated weights done with the GPUs' copy engines instead of a collective kernel: every
+    rank maps the flat buffer of every peer into its own GPU's address space (CUDA IPC with peer access) and PULLS
+    the peers' pieces of a bucket with plain device-to-device copies over NVLink, issued on its own GPU.  Nothing runs on the SMs, so the step of the next bucket keeps all of
+    them, and a peer copy moves more bytes per second than the NCCL all-gather does here.
+
+    Ordering between ranks comes from one-element all-reduces (NCCL, a few microseconds): a rank may read a peer's
+    piece of bucket b only after the peer has finished stepping it, and nobody may start the next step (which
+    rewrites its own pieces) before every peer has pulled them.  One process per GPU, all GPUs of one box visible
+    to every process."""
+
+    def __init__(self, sharded: ShardedParams, group=None):
+        import ctypes as C
+        self.sharded, self.group = sharded, group
+        self._lib = _lib.load()
+        handle = C.create_string_buffer(64)
+        offset = C.c_uint64(0)
+        with torch.cuda.device(sharded.flat.device):
+            _lib.check(self._lib.came_b200_ipc_export(sharded.flat.data_ptr(), handle, C.byref(offset)))
+            exported = [None] * sharded.world_size
+            dist.all_gather_object(exported, (handle.raw, int(offset.value)), group=group)
+            self.bases = [None] * sharded.world_size      # mapped allocations of the peers (to unmap)
+            self.peer_ptr = [0] * sharded.world_size      # address of each peer's flat buffer in this process
+            for r, (raw, off) in enumerate(exported):
+                if r == sharded.rank:
+                    continue
+                base = C.c_void_p()
+                _lib.check(self._lib.came_b200_ipc_open(raw, C.byref(base)))
+                self.bases[r] = base
+                self.peer_ptr[r] = base.value + off
+        self.flag = torch.zeros(1, dtype=torch.float32, device=sharded.flat.device)
+        self.side = torch.cuda.Stream(device=sharded.flat.device)
+
+    def close(self) -> None:
+        for r, base in enumerate(getattr(self, "bases", [])):
+            if base is not None:
+                self._lib.came_b200_ipc_close(base)
+                self.bases[r] = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def pull_bucket(self, b: int) -> None:
+        """Enqueue (on a side stream) the copies that bring every peer's piece of bucket b into the local buffer.
+        Call it after this rank's step of bucket b has been enqueued on the current stream."""
+        s = self.sharded
+        ready = dist.all_reduce(self.flag, group=self.group, async_op=True)   # every rank's bucket b is stepped
+        with torch.cuda.stream(self.side):
+            ready.wait()
+            n = s.piece_len[b]
+            for k in range(1, s.world_size):
+                r = (s.rank + k) % s.world_size          # start with a different peer on every rank
+                lo = s.bucket_off[b] + r * n
+                # issued from THIS GPU's side (its copy engine pulls): a copy issued on the source GPU from this
+                # process would wait for time slices between the kernels of the process that owns that GPU
+                esz = s.flat.element_size()
+                _lib.check(self._lib.came_b200_peer_copy_async(
+                    s.flat.data_ptr() + lo * esz, self.peer_ptr[r] + lo * esz, n * esz, -1, self.side.cuda_stream))
+
+    def finish(self) -> None:
+        """Current stream: wait for the pulls, then for every peer to have finished pulling from this rank."""
+        torch.cuda.current_stream().wait_stream(self.side)
+        dist.all_reduce(self.flag, group=self.group)
+
+
 class ShardedStepper:
     """One optimizer per bucket over the tensors this rank owns; `step()` steps bucket after bucket and starts the
     all-gather of a bucket's updated weights as soon as its step kernels are enqueued, so that the gather of
-    bucket b travels over NVLink while bucket b+1 is being stepped."""
+    bucket b travels over NVLink while bucket b+1 is being stepped.  `gather_mode`: "nccl" (in-place
+    all_gather_into_tensor per bucket) or "peer" (copy-engine pulls over CUDA IPC mappings, see PeerGather)."""
 
-    def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer):
+    def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer, gather_mode: str = "nccl"):
+        if gather_mode not in ("nccl", "peer"):
+            raise ValueError("gather_mode must be 'nccl' or 'peer'")
         self.sharded = sharded
         self.opts = []
         for b in range(sharded.n_buckets):
             ps = [params_by_index[i] for i in sharded.owned_in_bucket(b)]
             self.opts.append(make_optimizer(ps) if ps else None)
+        self.peer = PeerGather(sharded) if gather_mode == "peer" and sharded.world_size > 1 else None
 
     def step(self, gather: bool = True):
         works = []
@@ -126,9 +200,25 @@ class ShardedStepper:
             if opt is not None:
                 opt.step()
             if gather and self.sharded.world_size > 1:
-                works.append(self.sharded.all_gather_bucket(b, async_op=True))
+                if self.peer is not None:
+                    self.peer.pull_bucket(b)
+                else:
+                    works.append(self.sharded.all_gather_bucket(b, async_op=True))
         for w in works:
             w.wait()
+        if gather and self.peer is not None:
+            self.peer.finish()
+
+    def gather_only(self):
+        """The exchange alone (every bucket), for timing."""
+        if self.sharded.world_size == 1:
+            return
+        if self.peer is not None:
+            for b in range(self.sharded.n_buckets):
+                self.peer.pull_bucket(b)
+            self.peer.finish()
+        else:
+            self.sharded.all_gather()
 
     @property
     def last_step_launches(self) -> int:

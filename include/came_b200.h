@@ -204,6 +204,28 @@ int came_b200_step_vector_noalloc(void* p, const void* g, void* m, float* m_absm
                                   int64_t n, int mode, int p_dtype, int g_dtype, uint32_t flags,
                                   const CameHyper* hyper, came_stream_t stream);
 
+/*
+ * Multi-GPU weight exchange (no counterpart in the reference, which is single-GPU): one plain asynchronous
+ * device-to-device copy of `bytes` from `src` (memory of GPU `src_device`, mapped into this process, e.g. through
+ * a CUDA IPC handle) to `dst` (memory of the current device) on `stream`, a stream of the current device.  The copy
+ * is issued from the destination side, so it runs on the destination GPU's copy engine and never waits for a time
+ * slice on the source GPU, which another process keeps busy.  Peer access to `src_device` is enabled on first use;
+ * pass -1 when `src` was mapped by came_b200_ipc_open (which enables it itself).
+ */
+int came_b200_peer_copy_async(void* dst, const void* src, size_t bytes, int src_device, came_stream_t stream);
+
+/*
+ * Mapping another process's device buffer for came_b200_peer_copy_async (CUDA IPC, plain cudaMalloc memory only).
+ * export: handle of the allocation that contains `ptr` and the offset of `ptr` inside it; send both to the peer
+ *         process by any means.  open: maps that allocation into the CURRENT device's address space with peer
+ *         access (the current device is the one that will pull) and returns its base; the buffer is at
+ *         base + offset.  close: unmaps it.  The exporting process must keep the allocation alive meanwhile.
+ */
+#define CAME_B200_IPC_HANDLE_BYTES 64
+int came_b200_ipc_export(const void* ptr, unsigned char handle[CAME_B200_IPC_HANDLE_BYTES], uint64_t* offset);
+int came_b200_ipc_open(const unsigned char handle[CAME_B200_IPC_HANDLE_BYTES], void** base);
+int came_b200_ipc_close(void* base);
+
 /* error codes */
 #define CAME_OK 0
 #define CAME_E_INVALID (-1)   /* bad argument / descriptor; see came_b200_last_error() */

@@ -1,0 +1,71 @@
+"""Two ranks on two GPUs of one box: the copy-engine gather (CUDA IPC mappings, plain device-to-device copies)
+must leave exactly the bytes the NCCL all-gather leaves.  Skipped on a box with a single GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(256, 512), (384, 1024), (128, 192), (4096,), (300,), (512, 256), (64, 64), (1024,)]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import came_b200
+        from came_b200.partition import ShardedParams, ShardedStepper
+        dev = torch.device("cuda", rank)
+        results = {}
+        for mode in ("nccl", "peer"):
+            sp = ShardedParams(SHAPES, torch.bfloat16, dev, world, rank, buckets=2)
+            gen = torch.Generator(device=dev).manual_seed(3)
+            for v in sp.views:
+                v.copy_((torch.randn(v.shape, generator=gen, device=dev) * 0.02).bfloat16())
+            params = {i: torch.nn.Parameter(sp.views[i]) for i in sp.owned}
+            ggen = torch.Generator(device=dev).manual_seed(17)
+            grads = {i: (torch.randn(SHAPES[i], generator=ggen, device=dev) * 1e-2).bfloat16() for i in range(len(SHAPES))}
+            for i, p in params.items():
+                p.grad = grads[i].clone()
+            st = ShardedStepper(sp, params, lambda ps: came_b200.CAME8bit(ps, lr=1e-3), gather_mode=mode)
+            for _ in range(3):
+                st.step()
+            torch.cuda.synchronize()
+            results[mode] = sp.flat.clone()
+            dist.barrier()
+        same = torch.equal(results["nccl"], results["peer"])
+        flag = torch.tensor([1.0 if same else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            out.put(bool(flag.item() == 1.0))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_gather_equals_nccl_all_gather():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    for p in procs:
+        if p.is_alive():          # never by pattern: these are the exact processes started above
+            p.terminate()
+        assert p.exitcode == 0
+    assert out.get(timeout=10) is True
