@@ -276,7 +276,7 @@ def run_gpu(args):
     headline = cls_name == "CAME8bit"          # the per-kernel byte table below describes the tile-layout step
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
-    n_buckets = args.buckets if args.buckets > 0 else (4 if world > 1 else 1)
+    n_buckets = args.buckets if args.buckets > 0 else ({1: 1, 2: 8}.get(world, 4))
     sp = ShardedParams(shapes, pdtype, dev, world, rank, buckets=n_buckets)
     gen = torch.Generator(device=dev).manual_seed(1234)
     # every rank initialises every weight identically (same seed), as after a broadcast at start-up
@@ -450,7 +450,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--buckets", type=int, default=0, help="all-gather buckets at N > 1 (0: 4 when N > 1, else 1)")
+    ap.add_argument("--buckets", type=int, default=0, help="exchange buckets at N > 1 (0: 8 at N = 2, 4 above, 1 at N = 1)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                     help="exchange of updated weights at N > 1: copy-engine pulls over CUDA IPC mappings, or NCCL all-gather")
     ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
