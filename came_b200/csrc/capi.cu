@@ -41,7 +41,6 @@ struct LaunchItem {
     KernelKey key;
     size_t work_off;   // in Work units from the start of the work region
     int n;
-    size_t extra;      // fused first pass: largest staged slot (bytes) among the tensors of the launch
 };
 
 inline int elem_bytes(int dt) { return dt == CAME_DT_F32 ? 4 : 2; }

@@ -1,7 +1,8 @@
 // Tile-layout (CAME8bit / CAME8bit2D) momentum and apply passes for matrices whose column count is a
 // multiple of 64 and whose buffers are 16-byte aligned.
 //
-// Persistent CTAs (one per SM: 16 consumer warps + 1 producer warp) walk a strided share of the work list.  A work item is a tile of
+// Persistent CTAs (one per SM: 16 computing warps, one or two copy-issuing warps and, in the momentum pass, a
+// helper warp) walk a strided share of the work list.  A work item is a tile of
 // 128 rows x up to 1024 columns, consumed in 8 bands of 16 rows.  Bands are staged in shared memory by bulk
 // asynchronous copies (TMA, one copy per row per operand: 2 KB / 1 KB, the size at which the copy engine
 // reaches full bandwidth) through a ring of mbarriers that runs ahead across item boundaries.  Arithmetic
@@ -135,9 +136,9 @@ __device__ __forceinline__ WideItem wide_item(const StepArgs& a, const Work& w, 
     return it;
 }
 
-// Warps 0..15 consume (compute); warp 16 produces: it only issues the copies, because a bulk-copy instruction
-// blocks while the copy engine's queue is full and a band's 32 copies keep it busy for about as long as the
-// consumers need for a band.  Per ring slot there is a "full" barrier (the producer's expect_tx + the copies'
+// Warps 0..15 consume (compute); the warps after them produce: they only issue the copies, because a bulk-copy
+// instruction blocks while the copy engine's queue is full and a band's 32 copies keep a warp busy for about as long
+// as the consumers need for a band.  Per ring slot there is a "full" barrier (the producer's expect_tx + the copies'
 // bytes) and an "empty" barrier (one arrival per consumer warp).  Nobody synchronises CTA-wide inside the band
 // loop; consumer warps may drift apart by up to STAGES-1 bands.  A waiter that times out raises `abort` in
 // shared memory; everybody polls it.
