@@ -412,7 +412,7 @@ def run_gpu(args):
             "tensors every step; 54 GB touched per step, far above the 126 MB L2)",
             "config": {"workload": args.workload, "optimizer": cls_name, "param_dtype": dtype_name,
                        "tensors": len(shapes), "elements": total_elems,
-                       "parallelism": f"ownership x{world}, {n_buckets} buckets, gather of bucket b ({args.gather}) overlapped "
+                       "parallelism": f"ownership x{world}, {n_buckets} buckets, gather of bucket b ({stepper.gather_mode}) overlapped "
                                       f"with the step of bucket b+1" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2"},
             "roofline": roofline,
@@ -431,7 +431,7 @@ def run_gpu(args):
                 "note": "value / ms_per_step time the overlapped step + all-gather; the two legs below are timed alone",
                 "step_only_ms": ms_step_only, "step_only_gelem_s": total_elems / (ms_step_only * 1e-3) / 1e9,
                 "all_gather_ms": ag_ms, "all_gather_gbs_in": sp.gathered_bytes_per_rank() / (ag_ms * 1e-3) / 1e9,
-                "gather": args.gather, "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world)}
+                "gather": stepper.gather_mode, "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world)}
         if world == 1 and not args.no_cpu_baseline:
             dt, elems = cpu_step_time(2, 1)
             line["cpu_baseline"] = {"value": elems / dt / 1e9, "unit": "Gelem/s", "cores": torch.get_num_threads(),
@@ -451,8 +451,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buckets", type=int, default=0, help="exchange buckets at N > 1 (0: 8 at N = 2, 4 above, 1 at N = 1)")
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
-                    help="exchange of updated weights at N > 1: copy-engine pulls over CUDA IPC mappings, or NCCL all-gather")
+    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl"],
+                    help="exchange of updated weights at N > 1: copy-engine pulls over CUDA IPC mappings (auto: when every rank "
+                         "can map every peer, else NCCL), or NCCL all-gather")
     ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
                     help="llama7b: the benchmark workload (BASELINE config 3); profile: a small case of the same kernels "
                          "for ncu; the others are BASELINE configs 2, 4 and 5")

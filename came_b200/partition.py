@@ -185,14 +185,32 @@ class ShardedStepper:
     all_gather_into_tensor per bucket) or "peer" (copy-engine pulls over CUDA IPC mappings, see PeerGather)."""
 
     def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer, gather_mode: str = "nccl"):
-        if gather_mode not in ("nccl", "peer"):
-            raise ValueError("gather_mode must be 'nccl' or 'peer'")
+        if gather_mode not in ("nccl", "peer", "auto"):
+            raise ValueError("gather_mode must be 'nccl', 'peer' or 'auto'")
         self.sharded = sharded
         self.opts = []
         for b in range(sharded.n_buckets):
             ps = [params_by_index[i] for i in sharded.owned_in_bucket(b)]
             self.opts.append(make_optimizer(ps) if ps else None)
-        self.peer = PeerGather(sharded) if gather_mode == "peer" and sharded.world_size > 1 else None
+        self.peer = None
+        self.gather_mode = "nccl"
+        if gather_mode != "nccl" and sharded.world_size > 1:
+            # "auto": use the copy-engine exchange when every rank could map every peer, else NCCL (all ranks agree)
+            err = None
+            try:
+                self.peer = PeerGather(sharded)
+            except Exception as e:      # noqa: BLE001 - any mapping failure means: not available here
+                err = e
+            ok = torch.tensor([0.0 if err else 1.0], device=sharded.flat.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 1.0:
+                self.gather_mode = "peer"
+            else:
+                if self.peer is not None:
+                    self.peer.close()
+                    self.peer = None
+                if gather_mode == "peer":
+                    raise RuntimeError(f"peer mapping of the parameter buffers failed on some rank: {err}")
 
     def step(self, gather: bool = True):
         works = []
