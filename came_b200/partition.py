@@ -17,6 +17,7 @@ import torch.distributed as dist
 
 from . import _lib
 
+PEER_STREAMS = 1    # concurrent pulls per rank in the copy-engine exchange (two measured slower at 8 GPUs: 642 vs 707 GB/s)
 ALIGN_ELEMS = 128   # every tensor starts on a 256-byte boundary (bf16), keeping the 16-byte vector paths
 
 
@@ -141,7 +142,9 @@ class PeerGather:
                 self.bases[r] = base
                 self.peer_ptr[r] = base.value + off
         self.flag = torch.zeros(1, dtype=torch.float32, device=sharded.flat.device)
-        self.side = torch.cuda.Stream(device=sharded.flat.device)
+        # side stream(s) of the pulls; with one, a rank reads one peer at a time and the peers are visited in an order
+        # rotated by rank, so that every source serves one reader at a time
+        self.sides = [torch.cuda.Stream(device=sharded.flat.device) for _ in range(PEER_STREAMS)]
 
     def close(self) -> None:
         for r, base in enumerate(getattr(self, "bases", [])):
@@ -160,21 +163,25 @@ class PeerGather:
         Call it after this rank's step of bucket b has been enqueued on the current stream."""
         s = self.sharded
         ready = dist.all_reduce(self.flag, group=self.group, async_op=True)   # every rank's bucket b is stepped
-        with torch.cuda.stream(self.side):
-            ready.wait()
-            n = s.piece_len[b]
+        for side in self.sides:
+            with torch.cuda.stream(side):
+                ready.wait()
+        n = s.piece_len[b]
+        esz = s.flat.element_size()
+        with torch.cuda.device(s.flat.device):
             for k in range(1, s.world_size):
                 r = (s.rank + k) % s.world_size          # start with a different peer on every rank
                 lo = s.bucket_off[b] + r * n
                 # issued from THIS GPU's side (its copy engine pulls): a copy issued on the source GPU from this
                 # process would wait for time slices between the kernels of the process that owns that GPU
-                esz = s.flat.element_size()
                 _lib.check(self._lib.came_b200_peer_copy_async(
-                    s.flat.data_ptr() + lo * esz, self.peer_ptr[r] + lo * esz, n * esz, -1, self.side.cuda_stream))
+                    s.flat.data_ptr() + lo * esz, self.peer_ptr[r] + lo * esz, n * esz, -1,
+                    self.sides[k % len(self.sides)].cuda_stream))
 
     def finish(self) -> None:
         """Current stream: wait for the pulls, then for every peer to have finished pulling from this rank."""
-        torch.cuda.current_stream().wait_stream(self.side)
+        for side in self.sides:
+            torch.cuda.current_stream().wait_stream(side)
         dist.all_reduce(self.flag, group=self.group)
 
 
