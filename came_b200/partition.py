@@ -234,6 +234,29 @@ class ShardedStepper:
         if gather and self.peer is not None:
             self.peer.finish()
 
+    # -- sharded checkpoint: every rank saves and restores the state of the tensors it owns -------------------
+    def state_dict(self) -> dict:
+        """This rank's shard: the `state_dict()` of each bucket's optimizer (None where the rank owns nothing in the
+        bucket) together with the ownership map it belongs to.  The weights themselves are not part of it (after a
+        step every rank holds all of them in `sharded.flat`)."""
+        s = self.sharded
+        return {"world_size": s.world_size, "rank": s.rank, "shapes": [list(x) for x in s.shapes],
+                "owners": list(s.owners), "bucket_of": list(s.bucket_of),
+                "buckets": [None if o is None else o.state_dict() for o in self.opts]}
+
+    def load_state_dict(self, sd: dict) -> None:
+        s = self.sharded
+        same = (sd["world_size"] == s.world_size and sd["rank"] == s.rank and sd["owners"] == list(s.owners) and
+                sd["bucket_of"] == list(s.bucket_of) and [tuple(x) for x in sd["shapes"]] == s.shapes)
+        if not same:
+            raise ValueError("this shard was saved under a different ownership partition (world size, rank, shapes or "
+                             "bucket assignment differ); re-shard it before loading")
+        for o, b in zip(self.opts, sd["buckets"]):
+            if (o is None) != (b is None):
+                raise ValueError("bucket layout of the shard does not match")
+            if o is not None:
+                o.load_state_dict(b)
+
     def gather_only(self):
         """The exchange alone (every bucket), for timing."""
         if self.sharded.world_size == 1:
