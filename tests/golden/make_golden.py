@@ -82,7 +82,7 @@ def _bits(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of tukisuwa/CAME (the directory that holds came_pytorch/)")
     args = ap.parse_args()
     sys.dont_write_bytecode = True
     sys.path.insert(0, args.reference)
