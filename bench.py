@@ -277,6 +277,7 @@ def run_gpu(args):
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
     n_buckets = args.buckets if args.buckets > 0 else ({1: 1, 2: 8}.get(world, 4))
+    # equal buckets (a half-size first and last bucket measured no better: 11.76 against 11.56 ms at N = 2)
     sp = ShardedParams(shapes, pdtype, dev, world, rank, buckets=n_buckets)
     gen = torch.Generator(device=dev).manual_seed(1234)
     # every rank initialises every weight identically (same seed), as after a broadcast at start-up

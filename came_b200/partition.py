@@ -21,16 +21,21 @@ PEER_STREAMS = 1    # concurrent pulls per rank in the copy-engine exchange (two
 ALIGN_ELEMS = 128   # every tensor starts on a 256-byte boundary (bf16), keeping the 16-byte vector paths
 
 
-def assign_owners(numels, world_size: int):
+def assign_owners(numels, world_size: int, weights=None):
     """Greedy longest-processing-time assignment of tensors to ranks by element count.
-    Deterministic: ties go to the lower tensor index, then to the lower rank."""
+    Deterministic: ties go to the lower tensor index, then to the lower rank.  `weights` (one positive number per
+    rank) asks for loads in those proportions instead of equal ones."""
     if world_size <= 0:
         raise ValueError("world_size must be positive")
+    if weights is None:
+        weights = [1.0] * world_size
+    if len(weights) != world_size or any(w <= 0 for w in weights):
+        raise ValueError("weights must give one positive number per rank")
     order = sorted(range(len(numels)), key=lambda i: (-int(numels[i]), i))
     load = [0] * world_size
     owners = [0] * len(numels)
     for i in order:
-        r = min(range(world_size), key=lambda k: (load[k], k))
+        r = min(range(world_size), key=lambda k: ((load[k] + int(numels[i])) / weights[k], k))
         owners[i] = r
         load[r] += int(numels[i])
     return owners
@@ -50,9 +55,12 @@ class ShardedParams:
 
     Layout: [bucket][owner rank][that rank's tensors of the bucket, padded to the bucket's piece length].
     With one bucket this is the plain "slice per owner" layout.  With several, bucket b of every rank can be
-    gathered (one contiguous in-place all-gather) while the ranks are still stepping bucket b+1."""
+    gathered (one contiguous in-place all-gather) while the ranks are still stepping bucket b+1.  `bucket_weights`
+    sets the relative sizes of the buckets (a small first bucket starts the exchange early, a small last one
+    leaves a short tail after the last step)."""
 
-    def __init__(self, shapes, dtype: torch.dtype, device, world_size: int, rank: int, owners=None, buckets: int = 1):
+    def __init__(self, shapes, dtype: torch.dtype, device, world_size: int, rank: int, owners=None, buckets: int = 1,
+                 bucket_weights=None):
         self.shapes = [tuple(s) for s in shapes]
         self.world_size, self.rank = int(world_size), int(rank)
         self.n_buckets = max(1, int(buckets))
@@ -64,7 +72,7 @@ class ShardedParams:
         self.bucket_of = [0] * len(self.shapes)
         for r in range(world_size):
             mine = [i for i, o in enumerate(self.owners) if o == r]
-            sub = assign_owners([numels[i] for i in mine], self.n_buckets)
+            sub = assign_owners([numels[i] for i in mine], self.n_buckets, bucket_weights)
             for i, b in zip(mine, sub):
                 self.bucket_of[i] = b
         # offsets inside each (bucket, rank) cell

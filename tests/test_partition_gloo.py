@@ -105,3 +105,13 @@ def test_step_then_all_gather_matches_single_process(tmp_path):
     for r in range(world):
         for a, b in zip(got[r], want):
             assert torch.equal(a, b)
+
+
+def test_weighted_assignment_follows_the_weights():
+    owners = assign_owners([10] * 60, 4, [0.5, 1.0, 1.0, 0.5])
+    load = [sum(10 for o in owners if o == r) for r in range(4)]
+    assert load == [100, 200, 200, 100]
+    with pytest.raises(ValueError):
+        assign_owners([1, 2], 2, [1.0])
+    sp = ShardedParams(SHAPES, torch.float32, "cpu", world_size=1, rank=0, buckets=3, bucket_weights=[1.0, 2.0, 1.0])
+    assert sorted(i for b in range(3) for i in sp.owned_in_bucket(b)) == list(range(len(SHAPES)))
