@@ -248,6 +248,57 @@ def run_reference(args):
     emit(line)
 
 
+def run_reference_ext(args):
+    """Informational GPU baseline: the reference's own CUDA operators (its extension compiled for sm_100 by
+    oracle/build_ref.py) stepping the same workload on the same GPU, one operator call sequence per tensor as the
+    reference's optimizer classes issue them.  Not the contract's reference arm (that is the CPU leg above)."""
+    from oracle import ref_ext
+    ext = ref_ext.load()
+    if ext is None:
+        emit({"impl": "reference_ext", "unavailable": "oracle/_ref/came_cuda_ext.so has not been built (oracle/build_ref.py)"})
+        return
+    shape_fn, cls_name, dtype_name, betas = WORKLOADS[args.workload]
+    layout2d = {"CAME8bit": "tile", "CAME8bit2D": "tile", "CAME8bitFull": "flat", "CAME8bitMemory": "flat",
+                "CAMECUDA": "fp"}[cls_name]
+    shapes = [s for s in shape_fn() if len(s) == 2 or layout2d != "fp"]     # CAMECUDA steps 1-D tensors with torch ops
+    pdtype = getattr(torch, dtype_name)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    scale_gen = torch.Generator().manual_seed(7)
+    hyper = dict(HYPER, betas=betas)
+    ps, gs, sts = [], [], []
+    for s in shapes:
+        p = (torch.randn(s, generator=gen, device=dev) * 0.02).to(pdtype)
+        sc = 10.0 ** float(torch.empty(1).uniform_(-5, -2, generator=scale_gen))
+        ps.append(p)
+        gs.append((torch.randn(s, generator=gen, device=dev) * sc).to(pdtype))
+        sts.append(ref_ext.init_state(p, layout2d if len(s) == 2 else "flat", update_f16=cls_name == "CAME8bitMemory"))
+
+    def step():
+        for p, g, st in zip(ps, gs, sts):
+            ref_ext.step(ext, p, g, st, hyper)
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    elems = sum(math.prod(s) for s in shapes)
+    emit({"impl": "reference_ext", "metric": f"optimizer-step Gelem/s ({cls_name}, {args.workload})",
+          "value": elems / (ms * 1e-3) / 1e9, "unit": "Gelem/s", "n_gpus": 1, "steps": args.steps,
+          "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
+          "data": "synthetic (seeded)", "config": {"workload": args.workload, "optimizer": cls_name,
+                                                   "param_dtype": dtype_name, "tensors": len(shapes), "elements": elems},
+          "note": "reference extension (came_kernels.cu, --use_fast_math, sm_100), operator calls per tensor as "
+                  "its optimizer classes issue them; device time"})
+
+
 # ------------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------------
@@ -449,7 +500,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_ext"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buckets", type=int, default=0, help="exchange buckets at N > 1 (0: 8 at N = 2, 4 above, 1 at N = 1)")
     ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl"],
@@ -468,6 +519,8 @@ def main():
     os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference_ext":
+        run_reference_ext(args)
     else:
         run_gpu(args)
 

@@ -178,7 +178,8 @@ size_t count_work(const CameTensorDesc* descs, int n) {
         }
         w += 2 * (size_t)g.tiles_r * g.tiles_c;      // sq_partials, sumsq
         w += 2 * (size_t)(g.nbR + g.nbC);            // two vector finalizes
-        w += 1;                                      // s_finalize
+        // clip finalize: one CTA per S_FIN_CHUNK entries of the factor vectors on the staged momentum path
+        w += vec_flags(descs[i]).p2 == 2 ? (size_t)std::max<int64_t>(1, cdiv(g.R + g.C, S_FIN_CHUNK)) : (size_t)1;
         w += (size_t)g.ptiles_r * g.ptiles_c;        // moment
         if (descs[i].mode == CAME_MODE_FLAT8)
             w += (size_t)(g.nbR + g.nbC) + std::max((size_t)g.flat_chunks, (size_t)g.ptiles_r * g.ptiles_c);

@@ -17,7 +17,6 @@
 #include "launch.h"
 #include "pipeline.cuh"
 
-#include <cstdio>
 #include <type_traits>
 
 namespace came {

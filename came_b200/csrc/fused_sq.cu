@@ -15,7 +15,6 @@
 #include "launch.h"
 #include "pipeline.cuh"
 
-#include <cstdio>
 #include <algorithm>
 #include <cstdlib>
 

@@ -9,15 +9,16 @@ root, round-half-even), what the reference computes on each of its paths.  The
 reference keeps several slightly different variants of the same algorithm; each
 one is a ``Semantics`` preset below, citing the reference lines it follows.
 
-Pinning: the reference ships no tests or golden vectors.  The presets ``CAME``,
-``CUDAFP_GENERIC`` and ``FLAT8_CPU`` are pinned against trajectories produced by
-running the reference's own Python classes on CPU (fixtures under
-``tests/golden``, generator script beside them); the blockwise codec is pinned
-bit-exactly against ``came_pytorch/blockwise_quantization.py``.  The presets
-``TILE8``, ``FLAT8`` and ``CUDAFP`` restate the reference's *CUDA* kernels, which
-cannot run where the fixtures are generated; they share every building block
-with the pinned presets and differ only in the guards / weight-decay form /
-momentum source listed in the preset, read off ``came_kernels.cu``.
+Pinning: the reference ships no tests or golden vectors, so every preset is pinned
+against outputs of the reference itself.  ``CAME``, ``CUDAFP_GENERIC`` and
+``FLAT8_CPU`` against trajectories of the reference's own Python classes run on CPU
+(``tests/golden/traj_<class>_<case>.npz``, generator ``tests/golden/make_golden.py``);
+``TILE8``, ``FLAT8`` and ``CUDAFP``, which restate the reference's CUDA kernels,
+against trajectories of those kernels themselves: the reference's extension compiled
+for sm_100 by ``oracle/build_ref.py`` and run on a B200
+(``tests/golden/traj_gpu_<preset>_<case>.npz``, generator
+``tests/golden/make_golden_gpu.py``).  The blockwise codec is pinned bit-exactly
+against ``came_pytorch/blockwise_quantization.py``.
 """
 from __future__ import annotations
 

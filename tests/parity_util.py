@@ -8,16 +8,25 @@ import torch
 from oracle import came_oracle as orc
 
 
-def make_inputs(shapes, dtype, steps, seed, outlier_rows=True, grad_scale=1e-3):
+def make_inputs(shapes, dtype, steps, seed, outlier_rows=True, grad_scale=1e-3, per_tensor_scale=False,
+                student_t_frac=0.0):
+    """Seeded parameters N(0, 0.02^2) and per-step gradients N(0, grad_scale^2).
+    outlier_rows: every 7th row x100.  per_tensor_scale: each tensor's gradients are scaled by its own
+    10^U(-5, -2) instead of grad_scale (the Llama-7B benchmark configuration).  student_t_frac: that fraction of
+    the entries is replaced by grad_scale * StudentT(nu=2) draws (the Llama-1B drift configuration)."""
     rs = np.random.RandomState(seed)
     params = [torch.from_numpy((rs.standard_normal(s) * 0.02).astype(np.float32)).to(dtype) for s in shapes]
+    scales = [10.0 ** rs.uniform(-5, -2) if per_tensor_scale else grad_scale for _ in shapes]
     grads = []
     for _ in range(steps):
         gs = []
-        for s in shapes:
-            g = (rs.standard_normal(s) * grad_scale).astype(np.float32)
+        for s, sc in zip(shapes, scales):
+            g = (rs.standard_normal(s) * sc).astype(np.float32)
             if outlier_rows:
                 g[::7] *= 100.0
+            if student_t_frac > 0.0:
+                mask = rs.random_sample(s) < student_t_frac
+                g[mask] = (rs.standard_t(2.0, size=int(mask.sum())) * sc).astype(np.float32)
             gs.append(torch.from_numpy(g).to(dtype))
         grads.append(gs)
     return params, grads

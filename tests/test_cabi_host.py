@@ -154,3 +154,27 @@ def test_cpu_parameters_are_refused_not_silently_stepped():
     s.grad = torch.sparse_coo_tensor(torch.tensor([[0], [0]]), torch.tensor([1.0]), (8, 8))
     with pytest.raises(RuntimeError, match="sparse"):
         came_b200.CAME8bit([s], lr=1e-3).step()
+
+
+def test_work_list_never_overflows():
+    """plan_create sizes the work lists from the descriptors before it builds them; the two counts must agree for
+    every shape class (staged / generic kernels, fused / two-pass first pass, every layout).  With fake pointers
+    and no GPU the call gets past the work lists and fails at its first CUDA call."""
+    from came_b200 import _lib
+    lib = _lib.load()
+    shapes = [(4096, 32768), (128, 32000), (64, 20480), (1, 64), (130, 16448), (257, 8192), (100, 100),
+              (4096, 11008), (32000, 4096), (300, 72), (16, 65536 + 64), (5, 7), (2048, 256), (1000, 0), (70001, 0)]
+    ws = 1 << 40
+    for rows, cols in shapes:
+        for mode, flags in ((_lib.MODE_TILE8, 0), (_lib.MODE_FLAT8, 0), (_lib.MODE_FP32, _lib.F_SQ_CLAMP),
+                            (_lib.MODE_TILE8, _lib.F_SQ_CLAMP)):
+            if cols == 0 and mode == _lib.MODE_TILE8:
+                continue
+            for dt in (_lib.DT_BF16, _lib.DT_F32):
+                arr = (_lib.CameTensorDesc * 1)(_desc(rows=rows, cols=cols, mode=mode, flags=flags, p_dtype=dt, g_dtype=dt))
+                handle = C.c_void_p()
+                rc = lib.came_b200_plan_create(arr, 1, 0x10000000, ws, None, C.byref(handle))
+                msg = lib.came_b200_last_error().decode()
+                assert "overflow" not in msg, (rows, cols, mode, flags, dt, msg)
+                if rc == _lib.OK:
+                    lib.came_b200_plan_destroy(handle)
