@@ -35,13 +35,26 @@ KERNEL_BYTES = {
     "sumsq": 2.0,                             # g (only for tensors that take the two-pass form)
     "moment": 2.0 + 1.0 + 1.0 + 8.0 / 256,    # g, m read, m write, tile absmax read + write
     "apply": 1.0 + 2.0 + 2.0 + 4.0 / 256,     # m, p read, p write, tile absmax
+    # momentum + residual finalize + apply as one kernel: every operand once (the codes it re-reads are not counted)
+    "moment_apply": 2.0 + 1.0 + 1.0 + 2.0 + 2.0 + 8.0 / 256,
 }
 STEP_BYTES_2D = 2.0 + 2.0 + 2.0 + 1.0 + 1.0 + 8.0 / 256    # g, p r/w, m r/w, absmax   = 8.03 B/elem
 STEP_BYTES_1D = 2.0 + 4.0 + 2.0 + 2.0 + 16.0 / 256         # g, p r/w, m r/w, v r/w, two absmax = 10.06 B/elem
-# DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one launch on the
-# small `--workload profile` case, profiles/tile8_kernels_profile_workload.md); traffic grows in proportion to
-# the element count, so a full launch is this figure times the elements it processes
-NCU_TRAFFIC_BYTES_PER_ELEM = {"sq_partials": 2.05, "moment": 3.95, "apply": 4.80}
+
+
+def ncu_traffic_bytes_per_elem() -> dict:
+    """DRAM bytes per element of each kernel as ncu measured them (dram__bytes_read.sum + dram__bytes_write.sum of one
+    launch / matrix elements), read from the summary kept with the profiles; traffic grows in proportion to the
+    element count, so a full launch is this figure times the elements it processes."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "ncu_dram_bytes_per_element.txt")
+    if os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                parts = line.split()
+                if len(parts) >= 2 and not line.startswith("#"):
+                    out[parts[0]] = float(parts[1])
+    return out
 
 
 def llama7b_shapes():
@@ -439,7 +452,7 @@ def run_gpu(args):
             kernels[name] = ent
         if headline:
             dom = max((k for k in kernels if k in KERNEL_BYTES), key=lambda k: kernels[k]["share"])
-            traffic = NCU_TRAFFIC_BYTES_PER_ELEM.get(dom)
+            traffic = ncu_traffic_bytes_per_elem().get(dom)
             lps = kernels[dom]["launches_per_step"]
             roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
                         "frac": kernels[dom]["gbs"] / peak,

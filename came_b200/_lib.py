@@ -25,7 +25,7 @@ F_UPDATE_F16 = 1 << 7
 F_RSQRT_CLAMP = 1 << 8
 
 MAX_GROUPS = 64
-KERNEL_COUNT = 11
+KERNEL_COUNT = 12
 NOALLOC_MAX_ELEMS = 1 << 22
 OK, E_INVALID, E_WORKSPACE, E_CUDA, E_UNSUPPORTED = 0, -1, -2, -3, -4
 

@@ -24,6 +24,17 @@ thread_local char g_err[512] = "";
 // tests to compare the two implementations of a pass against each other)
 const bool g_disable_fast = [] { const char* e = getenv("CAME_B200_DISABLE_FAST"); return e && e[0] == '1'; }();
 
+// CAME_B200_WAVE_MB=n: run the momentum / apply passes in waves of tensors holding at most n MB of momentum state
+const size_t g_wave_bytes = [] { const char* e = getenv("CAME_B200_WAVE_MB"); return e ? (size_t)atol(e) << 20 : (size_t)0; }();
+
+// The fused momentum / apply kernel (fused_ma.cu).  CAME_B200_FUSED_MA=0 runs the three passes as separate launches.
+// CAME_B200_MA_LAG: momentum items of later tensors placed between a tensor's last momentum item and its apply items
+// (default: 5 per CTA; measured on Llama-7B shapes: 2 per CTA leaves the apply items waiting for the residual
+// finalize, from 5 on the kernel runs at the DRAM limit).
+// Read when a plan is created.
+bool fused_ma_enabled() { const char* e = getenv("CAME_B200_FUSED_MA"); return !(e && e[0] == '0'); }
+int env_int(const char* name, int dflt) { const char* e = getenv(name); return e ? atoi(e) : dflt; }
+
 int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -41,6 +52,8 @@ struct LaunchItem {
     KernelKey key;
     size_t work_off;   // in Work units from the start of the work region
     int n;
+    size_t work2_off;  // fused momentum / apply kernel: its F items
+    int n2;
 };
 
 inline int elem_bytes(int dt) { return dt == CAME_DT_F32 ? 4 : 2; }
@@ -130,7 +143,8 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
         s.fac = (d.mode == CAME_MODE_FLAT8 && vec_flags(d).flat != 2) ? take(2 * (size_t)(g.R + g.C)) : nullptr;
         if (vec_flags(d).p2 == 2) {
             s.res_eps_deferred = 1;
-            s.mfac = take((size_t)(g.R + g.C));
+            s.mfac = take((size_t)g.R);
+            s.mfac_c = take((size_t)g.C);
         }
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
@@ -164,7 +178,7 @@ int validate(const CameTensorDesc& d, int i) {
 }
 
 struct Layout {
-    size_t off_descs, off_scr, off_hyp, off_status, off_work, off_float, total;
+    size_t off_descs, off_scr, off_hyp, off_status, off_sync, off_work, off_float, total;
     size_t n_work;
 };
 
@@ -195,6 +209,7 @@ Layout layout(const CameTensorDesc* descs, int n) {
     L.off_scr = off;   off = align_up(off + (size_t)n * sizeof(Scratch));
     L.off_hyp = off;   off = align_up(off + (size_t)MAX_GROUPS * sizeof(CameHyper));
     L.off_status = off; off = align_up(off + sizeof(int));
+    L.off_sync = off;  off = align_up(off + (2 * (size_t)n + 8) * sizeof(int));   // fused kernel: per-tensor item counters, list cursors
     L.n_work = count_work(descs, n);
     L.off_work = off;  off = align_up(off + L.n_work * sizeof(Work));
     L.off_float = off;
@@ -235,6 +250,7 @@ struct came_plan {
     Layout L{};
     std::vector<LaunchItem> launches;
     int last_launches = 0;
+    bool has_fused_ma = false;
     bool timing = false;
     struct Timed { int kernel; cudaEvent_t t0, t1; };
     std::vector<Timed> timed;
@@ -386,18 +402,82 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_S_FINALIZE, is2d, nokey, [&](int i) {
         return vf[i].p2 == 2 ? std::max<int64_t>(1, cdiv(D[i].rows + D[i].cols, S_FIN_CHUNK)) : (int64_t)1;
     });
-    build(KID_MOMENT, is2d, [&](int i) { return Key{D[i].g_dtype, 0, D[i].mode, vf[i].p2}; },
-          [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
-    build(KID_RES_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
-    build(KID_APPLY, notflat, [&](int i) { return Key{0, D[i].p_dtype, D[i].mode, vf[i].p3}; },
-          [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
-    auto flat_generic = [&](int i) { return isflat(i) && vf[i].flat != 2; };
-    auto flat_staged = [&](int i) { return isflat(i) && vf[i].flat == 2; };
-    build(KID_FACTORS, flat_generic, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
-    build(KID_APPLY_FLAT, flat_generic, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, vf[i].flat}; },
-          [&](int i) { return geo[i].flat_chunks; });
-    build(KID_APPLY_FLAT, flat_staged, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 2}; },
-          [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
+    // Tensors of the tile layout on the staged path (same element type for g and p) take the fused kernel: their M, F
+    // and A items form one list, a tensor's F and A items delayed by `lag` momentum items of later tensors.
+    std::vector<char> fused(n_tensors, 0);
+    if (!g_disable_fast && fused_ma_enabled()) {
+        for (int i = 0; i < n_tensors; ++i)
+            fused[i] = D[i].cols != 0 && D[i].mode == CAME_MODE_TILE8 && vf[i].p2 == 2 && vf[i].p3 == 2 && D[i].g_dtype == D[i].p_dtype;
+    }
+    {
+        const int grid = persistent_grid_limit();
+        const size_t lag_a = (size_t)std::max(0, env_int("CAME_B200_MA_LAG", 5 * grid));
+        for (int dt = CAME_DT_F32; dt <= CAME_DT_BF16; ++dt) {
+            LaunchItem it{};
+            it.kernel = KID_MOMENT_APPLY;
+            it.key = KernelKey{dt, dt, CAME_MODE_TILE8, 2};
+            it.work_off = work.size();
+            struct Burst { size_t release; int tensor; };
+            std::vector<Burst> pend;      // apply bursts waiting for their place in the list
+            size_t next = 0, emitted = 0;
+            auto burst = [&](const Burst& b) {
+                const int64_t c = (int64_t)geo[b.tensor].ptiles_r * geo[b.tensor].ptiles_c;
+                for (int64_t k = 0; k < c; ++k) work.push_back(Work{b.tensor, (int32_t)(((uint32_t)MA_KIND_A << 28) | (uint32_t)k)});
+            };
+            for (int i = 0; i < n_tensors; ++i) {
+                if (!fused[i] || D[i].g_dtype != dt) continue;
+                const int64_t c = (int64_t)geo[i].ptiles_r * geo[i].ptiles_c;
+                for (int64_t k = 0; k < c; ++k) {
+                    work.push_back(Work{i, (int32_t)(((uint32_t)MA_KIND_M << 28) | (uint32_t)k)});
+                    ++emitted;
+                    while (next < pend.size() && pend[next].release <= emitted) burst(pend[next++]);
+                }
+                pend.push_back(Burst{emitted + lag_a, i});
+            }
+            while (next < pend.size()) burst(pend[next++]);
+            it.n = (int)(work.size() - it.work_off);
+            it.work2_off = work.size();
+            for (int i = 0; i < n_tensors; ++i) {
+                if (!fused[i] || D[i].g_dtype != dt) continue;
+                for (int k = 0; k < geo[i].nbR + geo[i].nbC; ++k) work.push_back(Work{i, k});
+            }
+            it.n2 = (int)(work.size() - it.work2_off);
+            if (it.n > 0) { plan->launches.push_back(it); plan->has_fused_ma = true; }
+        }
+    }
+    // The momentum pass, the residual finalize and the apply pass run wave by wave: a wave is a run of consecutive
+    // tensors whose momentum state together stays below `wave_bytes`, so that the codes the momentum pass writes are
+    // still in L2 when the apply pass reads them back (0: one wave, every pass covers all tensors).
+    std::vector<int> wave(n_tensors, 0);
+    int n_waves = 1;
+    if (g_wave_bytes > 0) {
+        size_t acc = 0;
+        int w = 0;
+        for (int i = 0; i < n_tensors; ++i) {
+            if (D[i].cols == 0) { wave[i] = 0; continue; }
+            const size_t mb = (size_t)D[i].rows * (size_t)D[i].cols * (D[i].mode == CAME_MODE_FP32 ? 4 : 1);
+            if (acc > 0 && acc + mb > g_wave_bytes) { ++w; acc = 0; }
+            wave[i] = w;
+            acc += mb;
+        }
+        n_waves = w + 1;
+    }
+    for (int w = 0; w < n_waves; ++w) {
+        auto in2d = [&](int i) { return is2d(i) && wave[i] == w && !fused[i]; };
+        auto in_notflat = [&](int i) { return notflat(i) && wave[i] == w && !fused[i]; };
+        build(KID_MOMENT, in2d, [&](int i) { return Key{D[i].g_dtype, 0, D[i].mode, vf[i].p2}; },
+              [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
+        build(KID_RES_FINALIZE, in2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
+        build(KID_APPLY, in_notflat, [&](int i) { return Key{0, D[i].p_dtype, D[i].mode, vf[i].p3}; },
+              [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
+        auto flat_generic = [&](int i) { return isflat(i) && vf[i].flat != 2 && wave[i] == w; };
+        auto flat_staged = [&](int i) { return isflat(i) && vf[i].flat == 2 && wave[i] == w; };
+        build(KID_FACTORS, flat_generic, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
+        build(KID_APPLY_FLAT, flat_generic, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, vf[i].flat}; },
+              [&](int i) { return geo[i].flat_chunks; });
+        build(KID_APPLY_FLAT, flat_staged, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 2}; },
+              [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
+    }
 
     if (work.size() > L.n_work) {
         delete plan;
@@ -476,7 +556,12 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
                reinterpret_cast<const CameHyper*>(plan->ws + plan->L.off_hyp),
                reinterpret_cast<int*>(plan->ws + plan->L.off_status)};
     const Work* wbase = reinterpret_cast<const Work*>(plan->ws + plan->L.off_work);
-    int launches = 0;
+    int* sync = reinterpret_cast<int*>(plan->ws + plan->L.off_sync);
+    if (plan->has_fused_ma) {      // the per-tensor item counters start every step at zero
+        e = cudaMemsetAsync(sync, 0, (2 * (size_t)plan->n_tensors + 8) * sizeof(int), st);
+        if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: counter reset: %s", cudaGetErrorString(e));
+    }
+    int launches = 0, fused_launches = 0;
     for (const LaunchItem& it : plan->launches) {
         came_plan::Timed tm{it.kernel, nullptr, nullptr};
         if (timing) {
@@ -488,6 +573,9 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
             e = launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         else if (it.kernel == KID_SQ_PARTIALS && it.key.variant == 2)
             e = launch_fused_sq(it.key, a, wbase + it.work_off, it.n, st);
+        else if (it.kernel == KID_MOMENT_APPLY)
+            e = launch_fused_ma(it.key, a, wbase + it.work_off, it.n, wbase + it.work2_off, it.n2, sync, sync + plan->n_tensors,
+                                sync + 2 * plan->n_tensors + 2 * (fused_launches++ % 3), st);      // two list cursors per launch (at most 3)
         else
             e = launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         if (timing) {
@@ -588,7 +676,7 @@ int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches) {
 const char* came_b200_kernel_name(int kernel) {
     static const char* names[CAME_KERNEL_COUNT] = {
         "sq_partials", "sq_finalize", "sumsq", "s_finalize", "moment", "res_finalize",
-        "apply", "factors", "apply_flat", "nf_partial", "nf_apply"};
+        "apply", "factors", "apply_flat", "nf_partial", "nf_apply", "moment_apply"};
     return (kernel >= 0 && kernel < CAME_KERNEL_COUNT) ? names[kernel] : "?";
 }
 

@@ -49,7 +49,8 @@ struct Scratch {
     int32_t nbR, nbC;             // ceil(rows/256), ceil(cols/256)
     int32_t fused_a;              // 1: the fused first pass runs (complete row sums, v_row and tpart come from it)
     int32_t fa_rb;                // fused first pass: rows per staged batch
-    float* mfac;                  // staged momentum pass: row factors / clip [R], then column factors [C]
+    float* mfac;                  // staged momentum pass: row factors r_i / clip [R]
+    float* mfac_c;                // staged passes: column factors [C], 16-byte aligned (c_j; after the residual finalize C'_j)
     int32_t sq_col_parts;         // column partial sets the first pass leaves (strips, or strips x 2 warp groups)
     int32_t res_eps_deferred;     // 1: the residual partials hold sums of (u-m)^2 only; eps1 is added per row / column
                                   //    by the finalize kernel (cols * eps1, rows * eps1)
@@ -308,6 +309,19 @@ __device__ __forceinline__ int quant_i8_fast(float x, float absmax, float inv) {
 // The reciprocal trick needs 1/absmax and the residual to stay normal; outside this range take the
 // plain division (uniform per block, so no divergence inside a warp's block).
 __device__ __forceinline__ bool recip_safe(float absmax) { return absmax > 1e-30f && absmax < 1e30f; }
+
+// ------------------------------------------------------------------------------------------
+// exponential moving average of a row / column statistic, with every rounding pinned (no contraction into
+// fused multiply-adds): two kernels that finalize the same vector then agree bit for bit, and the value is the one
+// the reference's separate multiply and add produce (came_kernels.cu:91, 546)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float ema_update(float old, float beta, float om, float x) {
+    return __fadd_rn(__fmul_rn(old, beta), __fmul_rn(om, x));
+}
+// (sum + n * eps) / n
+__device__ __forceinline__ float mean_plus_eps(float sum, float n, float eps) {
+    return __fdiv_rn(__fadd_rn(sum, __fmul_rn(n, eps)), n);
+}
 
 // ------------------------------------------------------------------------------------------
 // factor guards (one per reference code path, selected by CAME_F_* flags)

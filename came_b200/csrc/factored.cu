@@ -176,13 +176,11 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
             if (!is_col) {
                 const int parts = RES ? s.ptiles_c : s.tiles_c;
                 for (int t = 0; t < parts; ++t) acc += s.rowpart[(int64_t)t * R + idx];
-                if (RES && s.res_eps_deferred) acc += (float)C * h.eps1;
-                acc = acc / (float)C;
+                acc = (RES && s.res_eps_deferred) ? mean_plus_eps(acc, (float)C, h.eps1) : __fdiv_rn(acc, (float)C);
             } else {
                 acc = colsum;
-                if (fused) acc += (float)R * h.eps0;
-                if (RES && s.res_eps_deferred) acc += (float)R * h.eps1;
-                acc = acc / (float)R;
+                if (fused) acc = __fadd_rn(acc, __fmul_rn((float)R, h.eps0));
+                acc = (RES && s.res_eps_deferred) ? mean_plus_eps(acc, (float)R, h.eps1) : __fdiv_rn(acc, (float)R);
             }
             float old;
             if (quant) {
@@ -190,7 +188,7 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
             } else {
                 old = reinterpret_cast<const float*>(state)[idx];
             }
-            v = old * beta + om * acc;
+            v = ema_update(old, beta, om, acc);
             fresh[idx] = v;
         }
     }
@@ -290,7 +288,8 @@ __global__ void __launch_bounds__(THREADS) k_s_finalize(StepArgs a, const Work* 
         const int R = (int)d.rows, C = (int)d.cols;
         const int hi = min(R + C, (w.tile + 1) * S_FIN_CHUNK);      // this CTA's chunk of the R + C entries
         for (int i = w.tile * S_FIN_CHUNK + threadIdx.x; i < hi; i += THREADS)
-            s.mfac[i] = i < R ? row_factor(s.vr[i], mean, clamp) * inv_clip : col_factor(s.vc[i - R], clamp);
+            if (i < R) s.mfac[i] = row_factor(s.vr[i], mean, clamp) * inv_clip;
+            else s.mfac_c[i - R] = col_factor(s.vc[i - R], clamp);
     }
 }
 

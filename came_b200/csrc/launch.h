@@ -36,13 +36,20 @@ enum KernelId {
     KID_APPLY_FLAT,
     KID_NF_PARTIAL,
     KID_NF_APPLY,
+    KID_MOMENT_APPLY,      // momentum + residual finalize + apply of the tile layout as one kernel (fused_ma.cu)
     KID_COUNT
 };
+
+// kinds of work item of the fused momentum / apply kernel, carried in the top four bits of Work::tile
+enum { MA_KIND_M = 0, MA_KIND_F = 1, MA_KIND_A = 2, MA_KIND_END = 3 };
 
 cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                             cudaStream_t st);
 cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                               cudaStream_t st);
+// work: the M and A items in taking order; fwork: the F items in tensor order; next_item: two cursors (zeroed)
+cudaError_t launch_fused_ma(const KernelKey& key, const StepArgs& a, const Work* work, int n, const Work* fwork, int nf,
+                            int* mcount, int* fcount, int* next_item, cudaStream_t st);
 cudaError_t launch_fused_sq(const KernelKey& key, const StepArgs& a, const Work* work, int n, cudaStream_t st);
 // CTAs a persistent kernel launches: the SM count of the current device minus CAME_B200_RESERVED_SMS (environment,
 // read once; default 0).  Leaving a few SMs free lets small kernels of other streams (a collective's flag

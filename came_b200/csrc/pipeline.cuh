@@ -55,6 +55,29 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  : "memory");
 }
 
+// L2 eviction-priority policies for streams (read once: evict first) and for data another pass reads back soon
+// (evict last), and the copy / store forms that carry them
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void st_global_v2_hint(void* dst, uint2 v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v2.b32 [%0], {%1, %2}, %3;" ::"l"(dst), "r"(v.x), "r"(v.y), "l"(policy) : "memory");
+}
+
 // ---- packed fp32x2 (two independent IEEE fp32 operations per instruction, sm_100 FFMA2 / FADD2 / FMUL2) ----
 typedef float2 u64;   // a pair of fp32 values living in an aligned register pair
 #define F2ZERO make_float2(0.0f, 0.0f)

@@ -180,7 +180,7 @@ int came_b200_plan_last_launches(const came_plan_t* plan);
  * read_timing waits for the recorded events, adds their durations into ms[k] / launches[k]
  * (arrays of CAME_KERNEL_COUNT, zeroed by the callee) and forgets them.
  */
-#define CAME_KERNEL_COUNT 11
+#define CAME_KERNEL_COUNT 12
 int came_b200_plan_set_timing(came_plan_t* plan, int enable);
 int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches);
 const char* came_b200_kernel_name(int kernel);
