@@ -15,6 +15,7 @@ import argparse
 import json
 import math
 import os
+import platform
 import sys
 import threading
 import time
@@ -84,9 +85,9 @@ def profile_shapes():
 
 
 def cpu_sample_shapes():
-    """The bounded sample of the same workload that the CPU legs step: one tensor of each distinct matrix
-    shape inside a layer plus one norm vector (107 M elements)."""
-    return [(4096, 4096), (4096, 11008), (11008, 4096), (4096,)]
+    """The bounded sample of the Llama-7B workload that the CPU legs step: one tensor of each distinct shape with the
+    number of times the shape occurs in the set (the full-set time is extrapolated as sum of time(shape) x count)."""
+    return [((4096, 4096), 128), ((4096, 11008), 64), ((11008, 4096), 32), ((32000, 4096), 2), ((4096,), 65)]
 
 
 def gpt2_medium_shapes():
@@ -214,47 +215,90 @@ def physical_gpu_index(local: int) -> int:
 # ------------------------------------------------------------------------------------------------------
 
 def cpu_step_time(steps: int, warmup: int):
-    """Seconds per pass of the CPU restatement (tile layout for matrices, flat for vectors) over the sample."""
+    """The CPU restatement (tile layout for matrices, flat for vectors) over one tensor of each distinct Llama-7B shape.
+    Returns (seconds per step of the whole 291-tensor set, extrapolated as sum of time(shape) x count; elements of the
+    whole set; elements actually stepped per pass)."""
     from oracle import came_oracle as orc
-    shapes = cpu_sample_shapes()
+    sample = cpu_sample_shapes()
     gen = torch.Generator().manual_seed(0)
-    ps = [(torch.randn(s, generator=gen) * 0.02).bfloat16() for s in shapes]
-    gs = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes]
-    sems = [orc.TILE8 if len(s) == 2 else orc.FLAT8 for s in shapes]
-    sts = [orc.init_state(p, s) for p, s in zip(ps, sems)]
     hp = orc.Hyper(lr=HYPER["lr"], beta1=HYPER["betas"][0], beta2=HYPER["betas"][1], beta3=HYPER["betas"][2],
                    eps0=HYPER["eps"][0], eps1=HYPER["eps"][1], clip_threshold=HYPER["clip_threshold"],
                    weight_decay=HYPER["weight_decay"])
+    total_s, total_elems, stepped = 0.0, 0, 0
+    for shape, count in sample:
+        p = (torch.randn(shape, generator=gen) * 0.02).bfloat16()
+        g = (torch.randn(shape, generator=gen) * 1e-3).bfloat16()
+        sem = orc.TILE8 if len(shape) == 2 else orc.FLAT8
+        st = orc.init_state(p, sem)
+        for _ in range(warmup):
+            p = orc.step(p, g, st, hp, sem)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            p = orc.step(p, g, st, hp, sem)
+        dt = (time.perf_counter() - t0) / max(steps, 1)
+        total_s += dt * count
+        total_elems += math.prod(shape) * count
+        stepped += math.prod(shape)
+    return total_s, total_elems, stepped
 
-    def one():
+
+def cpu_cfg1_time(steps: int = 10):
+    """BASELINE config 1 as stated: one fp32 4096 x 4096 matrix and a 4096 bias, plain CAME (the pinned restatement of
+    came_pytorch/CAME.py:70-174), gradients N(0, 1e-3^2) with 1 % of the rows scaled x100, lr 2e-4, wd 1e-2, betas
+    (0.9, 0.999, 0.9999), `steps` steps, seed 0.  Returns (seconds per step, elements)."""
+    from oracle import came_oracle as orc
+    gen = torch.Generator().manual_seed(0)
+    shapes = [(4096, 4096), (4096,)]
+    ps = [torch.randn(s, generator=gen) * 0.02 for s in shapes]
+    sts = [orc.init_state(p, orc.CAME) for p in ps]
+    hp = orc.Hyper(lr=2e-4, beta1=0.9, beta2=0.999, beta3=0.9999, eps0=1e-30, eps1=1e-16, clip_threshold=1.0,
+                   weight_decay=1e-2)
+    rows = torch.randperm(4096, generator=gen)[:41]
+    t = 0.0
+    for k in range(steps):
+        gs = [torch.randn(s, generator=gen) * 1e-3 for s in shapes]
+        gs[0][rows] *= 100.0
+        t0 = time.perf_counter()
         for i in range(len(ps)):
-            ps[i] = orc.step(ps[i], gs[i], sts[i], hp, sems[i])
+            ps[i] = orc.step(ps[i], gs[i], sts[i], hp, orc.CAME)
+        t += time.perf_counter() - t0
+    return t / steps, sum(math.prod(s) for s in shapes)
 
-    for _ in range(warmup):
-        one()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        one()
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return dt, sum(math.prod(s) for s in shapes)
+
+CPU_SAMPLE_NOTE = ("one tensor of each distinct Llama-7B shape (4096x4096, 4096x11008, 11008x4096, 32000x4096, 4096) stepped by "
+                   "the CPU restatement; whole-set time extrapolated as sum of time(shape) x count (128, 64, 32, 2, 65)")
+
+
+def host_threads() -> int:
+    """All host cores: torch.distributed.run sets OMP_NUM_THREADS=1 for its workers, which would time the CPU leg on
+    one thread."""
+    n = os.cpu_count() or 1
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cores = host_threads()
     steps, warmup = max(1, args.steps), max(0, args.warmup)
-    steps, warmup = min(steps, 3), min(warmup, 1)          # several seconds per pass on 8 cores: keep the run to minutes
-    dt, elems = cpu_step_time(steps, warmup)
+    steps, warmup = min(steps, 2), 1          # seconds per pass on the host cores: keep the run to minutes (one cold pass first)
+    dt, elems, stepped = cpu_step_time(steps, warmup)
     value = elems / dt / 1e9
-    sample = "one 4096x4096, 4096x11008, 11008x4096 matrix and one 4096 vector of the Llama-7B set per step"
+    t1, e1 = cpu_cfg1_time(10)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "Gelem/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-        "config": {"workload": "llama7b_came8bit_bf16", "sample": sample, "elements_per_step": elems},
-        "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "config": {"workload": "llama7b", "optimizer": "CAME8bit", "param_dtype": "bfloat16", "tensors": 291,
+                   "elements": elems, "sample": CPU_SAMPLE_NOTE, "elements_stepped_per_pass": stepped,
+                   "ms_per_step_is": "extrapolated to the whole set"},
+        "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": cores, "kind": "port", "sample": CPU_SAMPLE_NOTE,
+                         "cfg1": {"value": e1 / t1 / 1e9, "unit": "Gelem/s", "ms_per_step": t1 * 1e3, "steps": 10,
+                                  "what": "BASELINE config 1: fp32 4096x4096 + 4096, plain CAME (restatement of "
+                                          "came_pytorch/CAME.py), 10 steps", "cores": cores,
+                                  "cpu": platform.processor() or platform.machine()}},
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -435,6 +479,17 @@ def run_gpu(args):
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te[0])
 
+    # once per run, outside any timed region: every rank must hold the same weights after the exchange
+    weights_identical = None
+    if world > 1:
+        bits = sp.flat.view(torch.int16 if sp.flat.element_size() == 2 else torch.int32).to(torch.int64)
+        cs = torch.stack([bits.sum(), (bits * bits).sum()])      # two checksums of the bit patterns
+        del bits
+        lo, hi = cs.clone(), cs.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        weights_identical = bool(torch.equal(lo, hi))
+
     # ---- report ----------------------------------------------------------------------------------------
     if rank == 0:
         peak, peak_src = peaks()
@@ -496,12 +551,20 @@ def run_gpu(args):
                 "note": "value / ms_per_step time the overlapped step + all-gather; the two legs below are timed alone",
                 "step_only_ms": ms_step_only, "step_only_gelem_s": total_elems / (ms_step_only * 1e-3) / 1e9,
                 "all_gather_ms": ag_ms, "all_gather_gbs_in": sp.gathered_bytes_per_rank() / (ag_ms * 1e-3) / 1e9,
-                "gather": stepper.gather_mode, "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world)}
+                "gather": stepper.gather_mode, "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world),
+                "exchange_floor_ms": sp.gathered_bytes_per_rank() / 770e9 * 1e3,
+                "exchange_frac_of_floor": (sp.gathered_bytes_per_rank() / 770e9 * 1e3) / ag_ms,
+                "weights_identical_on_all_ranks": weights_identical}
         if world == 1 and not args.no_cpu_baseline:
-            dt, elems = cpu_step_time(2, 1)
-            line["cpu_baseline"] = {"value": elems / dt / 1e9, "unit": "Gelem/s", "cores": torch.get_num_threads(),
-                                    "kind": "port", "sample": "one 4096x4096, 4096x11008, 11008x4096 matrix and one "
-                                    "4096 vector of the Llama-7B set, 2 timed passes of the CPU restatement"}
+            cores = host_threads()
+            dt, elems, _ = cpu_step_time(1, 1)
+            t1, e1 = cpu_cfg1_time(10)
+            line["cpu_baseline"] = {"value": elems / dt / 1e9, "unit": "Gelem/s", "cores": cores, "kind": "port",
+                                    "sample": CPU_SAMPLE_NOTE,
+                                    "cfg1": {"value": e1 / t1 / 1e9, "unit": "Gelem/s", "ms_per_step": t1 * 1e3, "steps": 10,
+                                             "what": "BASELINE config 1: fp32 4096x4096 + 4096, plain CAME (restatement "
+                                                     "of came_pytorch/CAME.py), 10 steps", "cores": cores,
+                                             "cpu": platform.processor() or platform.machine()}}
         emit(line)
     if world > 1:
         dist.barrier()

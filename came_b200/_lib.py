@@ -25,7 +25,7 @@ F_UPDATE_F16 = 1 << 7
 F_RSQRT_CLAMP = 1 << 8
 
 MAX_GROUPS = 64
-KERNEL_COUNT = 12
+KERNEL_COUNT = 13
 NOALLOC_MAX_ELEMS = 1 << 22
 OK, E_INVALID, E_WORKSPACE, E_CUDA, E_UNSUPPORTED = 0, -1, -2, -3, -4
 
@@ -79,6 +79,7 @@ SYMBOLS = {
     "came_b200_ipc_close": (C.c_int, [C.c_void_p]),
     "came_b200_plan_last_launches": (C.c_int, [C.c_void_p]),
     "came_b200_plan_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "came_b200_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "came_b200_plan_set_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "came_b200_plan_read_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "came_b200_kernel_name": (C.c_char_p, [C.c_int]),

@@ -98,7 +98,7 @@ Geometry geometry(const CameTensorDesc& d) {
     g.C = d.cols;
     g.nbR = (int)cdiv(g.R, QBLOCK);
     if (d.cols == 0) {
-        g.floats = align_up((size_t)g.nbR, 4);
+        g.floats = align_up((size_t)g.nbR + 1, 4);
         return g;
     }
     g.nbC = (int)cdiv(g.C, QBLOCK);
@@ -122,7 +122,7 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
     Scratch s{};
     s.nbR = g.nbR;
     if (d.cols == 0) {
-        s.spart = take((size_t)g.nbR);
+        s.spart = take((size_t)g.nbR + 1);      // block partials of sum u^2, then their sum
     } else {
         s.nbC = g.nbC;
         s.tiles_r = g.tiles_r; s.tiles_c = g.tiles_c;
@@ -187,7 +187,7 @@ size_t count_work(const CameTensorDesc* descs, int n) {
     for (int i = 0; i < n; ++i) {
         const Geometry g = geometry(descs[i]);
         if (descs[i].cols == 0) {
-            w += 2 * (size_t)g.nbR;
+            w += 2 * (size_t)g.nbR + 1;      // partial, apply; one reduce CTA
             continue;
         }
         w += 2 * (size_t)g.tiles_r * g.tiles_c;      // sq_partials, sumsq
@@ -382,6 +382,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     const auto& vf = plan->vflags;
 
     build(KID_NF_PARTIAL, is1d, [&](int i) { return Key{D[i].g_dtype, 0, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
+    build(KID_NF_REDUCE, is1d, nokey, [&](int) { return (int64_t)1; });
     build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
     auto fusedA = [&](int i) { return D[i].cols != 0 && vf[i].k == 2; };
     auto twopass = [&](int i) { return D[i].cols != 0 && vf[i].k != 2; };
@@ -569,7 +570,7 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
                 return fail(CAME_E_CUDA, "step: cudaEventCreate failed");
             cudaEventRecord(tm.t0, st);
         }
-        if (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY)
+        if (it.kernel == KID_NF_PARTIAL || it.kernel == KID_NF_APPLY || it.kernel == KID_NF_REDUCE)
             e = launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         else if (it.kernel == KID_SQ_PARTIALS && it.key.variant == 2)
             e = launch_fused_sq(it.key, a, wbase + it.work_off, it.n, st);
@@ -639,6 +640,15 @@ int came_b200_ipc_close(void* base) {
     return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "ipc_close: %s", cudaGetErrorString(e));
 }
 
+int came_b200_selftest_bounded_wait(int* device_words, came_stream_t stream) {
+    if (!device_words) return fail(CAME_E_INVALID, "selftest_bounded_wait: device_words is null");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(device_words, 0xff, 3 * sizeof(int), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(device_words, 0, sizeof(int), st);
+    if (e == cudaSuccess) e = launch_selftest_bounded_wait(device_words, device_words + 1, st);
+    return e == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "selftest_bounded_wait: %s", cudaGetErrorString(e));
+}
+
 int came_b200_plan_last_launches(const came_plan_t* plan) { return plan ? plan->last_launches : 0; }
 
 int came_b200_plan_status(came_plan_t* plan, came_stream_t stream, int* status) {
@@ -676,7 +686,7 @@ int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches) {
 const char* came_b200_kernel_name(int kernel) {
     static const char* names[CAME_KERNEL_COUNT] = {
         "sq_partials", "sq_finalize", "sumsq", "s_finalize", "moment", "res_finalize",
-        "apply", "factors", "apply_flat", "nf_partial", "nf_apply", "moment_apply"};
+        "apply", "factors", "apply_flat", "nf_partial", "nf_apply", "nf_reduce", "moment_apply"};
     return (kernel >= 0 && kernel < CAME_KERNEL_COUNT) ? names[kernel] : "?";
 }
 

@@ -606,6 +606,31 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
 }
 
 // ------------------------------------------------------------------------------------------------
+// self-test of the bounded wait: one CTA of two warps waits, through wide_wait with a small limit, on a barrier that
+// nothing ever completes.  The first warp to run out records STATUS_MBAR_TIMEOUT in *status and raises the CTA's abort
+// flag; the other one leaves at its next poll of the flag; the kernel returns.  Nothing is in flight, nothing faults.
+// ------------------------------------------------------------------------------------------------
+__global__ void k_selftest_bounded_wait(int* status, int* observed) {
+    __shared__ WideShared sh;
+    if (threadIdx.x == 0) {
+        mbar_init(&sh.full[0], 1);
+        sh.abort = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+    StepArgs a{nullptr, nullptr, nullptr, status};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // warp 0 runs out after 4096 polls; warp 1 has the full limit and must leave because of the abort flag
+    const bool ok = wide_wait(&sh.full[0], 0, &sh, a, lane, warp == 0 ? 4096u : MBAR_SPIN_LIMIT);
+    if (lane == 0) observed[warp] = ok ? 1 : 0;
+}
+
+cudaError_t launch_selftest_bounded_wait(int* status, int* observed, cudaStream_t st) {
+    k_selftest_bounded_wait<<<1, 64, 0, st>>>(status, observed);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------------
 template <typename T> static constexpr size_t moment_smem() {

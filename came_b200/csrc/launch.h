@@ -36,6 +36,7 @@ enum KernelId {
     KID_APPLY_FLAT,
     KID_NF_PARTIAL,
     KID_NF_APPLY,
+    KID_NF_REDUCE,
     KID_MOMENT_APPLY,      // momentum + residual finalize + apply of the tile layout as one kernel (fused_ma.cu)
     KID_COUNT
 };
@@ -60,6 +61,8 @@ void fused_sq_geometry(int64_t cols, int elem_bytes, int* groups, int* ng, int* 
 bool fused_sq_eligible(int64_t cols, int elem_bytes);
 cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                                cudaStream_t st);
+
+cudaError_t launch_selftest_bounded_wait(int* status, int* observed, cudaStream_t st);
 
 cudaError_t launch_quantize_blockwise(const float* src, void* q, float* absmax, int64_t n, bool is_signed,
                                       cudaStream_t st);

@@ -7,10 +7,10 @@
 // pre-planned memory schedule.  Those callers can hand over their tensors but cannot produce the workspace
 // that came_b200_plan_create asks for.
 //
-// The per-block partial sums that the two kernels of the 1-D step pass to each other therefore live in a
+// The per-block partial sums (and their total) that the kernels of the 1-D step pass to each other therefore live in a
 // file-scope device array of fixed size.  Consequences, all of them part of the contract:
 //   * the tensor may have at most CAME_B200_NOALLOC_MAX_ELEMS elements;
-//   * every GPU that loads the library carries the array (64 KiB) until the process exits;
+//   * every GPU that loads the library carries the array (64 KiB + one line) until the process exits;
 //   * all calls on a device share it: two calls whose kernels overlap on the GPU (different streams) race;
 //     calls on one stream are ordered and safe.  Nothing in it has to start at zero: a call first overwrites
 //     every entry it later reads, whatever the previous call left there;
@@ -29,7 +29,8 @@ void set_last_error(const char* msg);   // capi.cu
 constexpr int NOALLOC_MAX_BLOCKS = CAME_B200_NOALLOC_MAX_ELEMS / QBLOCK;   // 16384 partial sums = 64 KiB
 
 // In host code this name is only a handle for cudaGetSymbolAddress, not a device address.
-static __device__ __align__(256) float g_noalloc_partials[NOALLOC_MAX_BLOCKS];
+// 16384 block sums, then (one 256-byte line further) their total
+static __device__ __align__(256) float g_noalloc_partials[NOALLOC_MAX_BLOCKS + 64];
 
 struct NoallocArgs {
     void* p;
@@ -85,12 +86,19 @@ __global__ void __launch_bounds__(THREADS) k_noalloc_partial(NoallocArgs a) {
     if (threadIdx.x == 0) a.partials[b] = t;      // every entry the second kernel reads is written here first
 }
 
+// S = sum of the block sums, by one CTA in the fixed order the workspace path uses; kept behind the partials
+__global__ void __launch_bounds__(THREADS) k_noalloc_reduce(NoallocArgs a, int nblocks) {
+    __shared__ float red[33];
+    const float S = block_vector_sum(a.partials, nblocks, red);
+    if (threadIdx.x == 0) a.partials[NOALLOC_MAX_BLOCKS] = S;
+}
+
 __global__ void __launch_bounds__(THREADS) k_noalloc_apply(NoallocArgs a, int nblocks) {
     __shared__ float red[33];
     const int b = blockIdx.x;
     const int64_t idx = (int64_t)b * QBLOCK + threadIdx.x;
     const bool valid = idx < a.n;
-    const float S = block_vector_sum(a.partials, nblocks, red);
+    const float S = a.partials[NOALLOC_MAX_BLOCKS];
     const float clip = fmaxf(1.0f, sqrtf(S / (float)a.n) / a.h.clip_threshold);
     float g, v, u;
     noalloc_second_moment(a, b, idx, valid, g, v, u);
@@ -171,6 +179,7 @@ extern "C" int came_b200_step_vector_noalloc(void* p, const void* g, void* m, fl
     const int nblocks = (int)((n + QBLOCK - 1) / QBLOCK);
     cudaStream_t st = (cudaStream_t)stream;
     k_noalloc_partial<<<nblocks, THREADS, 0, st>>>(a);
+    k_noalloc_reduce<<<1, THREADS, 0, st>>>(a, nblocks);
     k_noalloc_apply<<<nblocks, THREADS, 0, st>>>(a, nblocks);
     return cudaGetLastError() == cudaSuccess ? CAME_OK : fail(CAME_E_CUDA, "step_vector_noalloc: kernel launch failed");
 }

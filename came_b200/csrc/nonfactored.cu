@@ -1,6 +1,7 @@
 // CAME step for 1-D (non-factored) tensors: two multi-tensor launches over blocks of 256 elements.
 //
 //   nf_partial : g, v        -> per-block partial of sum u^2,  u = g * rsqrt(v_new)
+//   nf_reduce  : partials    -> S = sum u^2 of a tensor (one CTA per tensor, fixed order)
 //   nf_apply   : g, v, m, p  -> v, m, p   (v_new and u are recomputed; no scratch tensor carries u)
 //
 // Reference: kCameNonfactoredSqUpdateAndQuant[TypedUpdate] came_kernels.cu:1013-1122 and
@@ -43,6 +44,14 @@ __global__ void __launch_bounds__(THREADS) k_nf_partial(StepArgs a, const Work* 
     if (threadIdx.x == 0) s.spart[w.tile] = t;
 }
 
+// S of one tensor, left behind its block partials: the apply CTAs read one float instead of summing all partials each
+__global__ void __launch_bounds__(THREADS) k_nf_reduce(StepArgs a, const Work* __restrict__ work) {
+    __shared__ float red[33];
+    const Scratch& s = a.scr[work[blockIdx.x].tensor];
+    const float S = block_vector_sum(s.spart, s.nbR, red);
+    if (threadIdx.x == 0) s.spart[s.nbR] = S;
+}
+
 template <typename TG, typename TP>
 __global__ void __launch_bounds__(THREADS) k_nf_apply(StepArgs a, const Work* __restrict__ work) {
     __shared__ float red[33];
@@ -55,7 +64,7 @@ __global__ void __launch_bounds__(THREADS) k_nf_apply(StepArgs a, const Work* __
     const bool valid = idx < d.rows;
     const bool quant = d.mode != CAME_MODE_FP32;
 
-    const float S = block_vector_sum(s.spart, s.nbR, red);
+    const float S = s.spart[s.nbR];
     const float clip = fmaxf(1.0f, sqrtf(S / (float)d.rows) / h.clip_threshold);
 
     float g, v, u;
@@ -109,6 +118,8 @@ cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs&
     if (kernel == KID_NF_PARTIAL) {
         fn = key.g_dtype == CAME_DT_F32 ? k_nf_partial<float>
              : key.g_dtype == CAME_DT_F16 ? k_nf_partial<__half> : k_nf_partial<__nv_bfloat16>;
+    } else if (kernel == KID_NF_REDUCE) {
+        fn = k_nf_reduce;
     } else if (kernel == KID_NF_APPLY) {
         fn = key.g_dtype == CAME_DT_F32 ? pick_apply_p<float>(key.p_dtype)
              : key.g_dtype == CAME_DT_F16 ? pick_apply_p<__half>(key.p_dtype) : pick_apply_p<__nv_bfloat16>(key.p_dtype);

@@ -144,9 +144,10 @@ struct WideShared {
 
 // Bounded wait that also gives up when another warp raised `abort`.  On its own timeout it records the failure
 // in the plan's status word and raises `abort`, so that every other waiter of the CTA leaves too.
-__device__ __forceinline__ bool wide_wait(uint64_t* bar, uint32_t parity, WideShared* sh, const StepArgs& a, int lane) {
+__device__ __forceinline__ bool wide_wait(uint64_t* bar, uint32_t parity, WideShared* sh, const StepArgs& a, int lane,
+                                          uint32_t limit = MBAR_SPIN_LIMIT) {
     volatile int* abort = &sh->abort;
-    for (uint32_t i = 0; i < MBAR_SPIN_LIMIT; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return *abort == 0;
         if ((i & 15u) == 15u && *abort) return false;
     }

@@ -260,17 +260,59 @@ class _CameB200Optimizer(torch.optim.Optimizer):
                     copy_backs.append(cb)
         return entries, hypers, copy_backs
 
+    def _hypers(self):
+        hypers = []
+        for group in self.param_groups:
+            hp = (group["lr"], group["betas"], group["eps"], group["clip_threshold"], group["weight_decay"])
+            hypers.append(make_hyper(*hp, python_scalars=False))
+            hypers.append(make_hyper(*hp, python_scalars=True))
+        return hypers
+
+    def _signature(self):
+        """What decides the tensor table of a step: per parameter its gradient's address, dtype and shape (None for a
+        parameter without gradient).  While it stays the same the plans of the previous step are stepped again
+        without rebuilding the per-tensor entries (hyper-parameters are re-read every step all the same)."""
+        sig = []
+        for group in self.param_groups:
+            for p in group["params"]:
+                g = p.grad
+                if g is None:
+                    sig.append(None)
+                elif g.is_sparse or not (g.is_contiguous() and p.is_contiguous()):
+                    return None            # slow path: raises / copies as the reference does
+                else:
+                    sig.append((p.data_ptr(), g.data_ptr(), g.dtype, p.shape))
+        return sig
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        sig = self._signature()
+        cached = getattr(self, "_step_cache", None)
+        if sig is not None and cached is not None and cached[0] == sig and cached[3] == len(self.param_groups):
+            _, plans, stepped_states, _ = cached
+            for st in stepped_states:
+                st["step"] += 1
+            hypers = self._hypers()
+            launches = 0
+            for plan in plans:
+                plan.step(hypers)
+                launches += plan.last_launches
+            self.last_step_launches = launches
+            return loss
+        self._step_cache = None
         entries, hypers, copy_backs = self._collect()
         if entries:
             self.last_step_launches = self._engine.step(entries, hypers)
         for p, p_data in copy_backs:
             p.data.copy_(p_data)
+        if entries and sig is not None and not copy_backs and not any(e.keep for e in entries):
+            stepped = [self.state[p] for g in self.param_groups for p in g["params"]
+                       if p.grad is not None and "step" in self.state[p]]
+            self._step_cache = (sig, list(self._engine.plans.values()), stepped, len(self.param_groups))
         return loss
 
     @torch.no_grad()
@@ -292,12 +334,7 @@ class _CameB200Optimizer(torch.optim.Optimizer):
         learning-rate schedule needs no re-capture.  (The reference's captured kernels carry these values as
         launch arguments and have to be captured again, CAME8bit2D.py:52-72.)  Call it before launching the
         replay that should see the new values."""
-        hypers = []
-        for group in self.param_groups:
-            hp = (group["lr"], group["betas"], group["eps"], group["clip_threshold"], group["weight_decay"])
-            hypers.append(make_hyper(*hp, python_scalars=False))
-            hypers.append(make_hyper(*hp, python_scalars=True))
-        self._engine.set_hyper(hypers)
+        self._engine.set_hyper(self._hypers())
 
     # -- checkpointing --------------------------------------------------------------------------
     def state_dict(self):
@@ -326,6 +363,11 @@ class _CameB200Optimizer(torch.optim.Optimizer):
             if st.get("_mode") == "full8bit" and st.get("factored", False) and "factored_row_q" in st:
                 bind_flat_views(st)
         self._engine.invalidate()
+        self._step_cache = None
+
+    def add_param_group(self, param_group):
+        super().add_param_group(param_group)
+        self._step_cache = None
 
 
 # ----------------------------------------------------------------------------------------------

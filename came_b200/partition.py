@@ -10,6 +10,7 @@ so a single in-place `all_gather_into_tensor` (ncclAllGather with sendbuff insid
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
@@ -134,25 +135,40 @@ class PeerGather:
         import ctypes as C
         self.sharded, self.group = sharded, group
         self._lib = _lib.load()
+        self.bases = [None] * sharded.world_size      # mapped allocations of the peers (to unmap)
+        self.peer_ptr = [0] * sharded.world_size      # address of each peer's flat buffer in this process
         handle = C.create_string_buffer(64)
         offset = C.c_uint64(0)
-        with torch.cuda.device(sharded.flat.device):
-            _lib.check(self._lib.came_b200_ipc_export(sharded.flat.data_ptr(), handle, C.byref(offset)))
+        on_gpu = sharded.flat.is_cuda
+        with (torch.cuda.device(sharded.flat.device) if on_gpu else contextlib.nullcontext()):
+            # Every rank takes part in the collective below whatever happened to its own export: a rank that failed
+            # sends None, and every rank then sees that the exchange is not available (no rank is left waiting in a
+            # collective the others skipped).
+            mine = None
+            if self._lib.came_b200_ipc_export(sharded.flat.data_ptr(), handle, C.byref(offset)) == _lib.OK:
+                mine = (handle.raw, int(offset.value))
             exported = [None] * sharded.world_size
-            dist.all_gather_object(exported, (handle.raw, int(offset.value)), group=group)
-            self.bases = [None] * sharded.world_size      # mapped allocations of the peers (to unmap)
-            self.peer_ptr = [0] * sharded.world_size      # address of each peer's flat buffer in this process
-            for r, (raw, off) in enumerate(exported):
-                if r == sharded.rank:
-                    continue
-                base = C.c_void_p()
-                _lib.check(self._lib.came_b200_ipc_open(raw, C.byref(base)))
-                self.bases[r] = base
-                self.peer_ptr[r] = base.value + off
+            dist.all_gather_object(exported, mine, group=group)
+            self.error = None
+            if any(e is None for e in exported):
+                self.error = "a rank could not export its parameter buffer"
+            else:
+                for r, (raw, off) in enumerate(exported):
+                    if r == sharded.rank:
+                        continue
+                    base = C.c_void_p()
+                    if self._lib.came_b200_ipc_open(raw, C.byref(base)) != _lib.OK:
+                        self.error = f"mapping the buffer of rank {r} failed: " + self._lib.came_b200_last_error().decode()
+                        break
+                    self.bases[r] = base
+                    self.peer_ptr[r] = base.value + off
+        if self.error:
+            return
         self.flag = torch.zeros(1, dtype=torch.float32, device=sharded.flat.device)
         # side stream(s) of the pulls; with one, a rank reads one peer at a time and the peers are visited in an order
         # rotated by rank, so that every source serves one reader at a time
         self.sides = [torch.cuda.Stream(device=sharded.flat.device) for _ in range(PEER_STREAMS)]
+        self.pulled = None        # pending: "every peer has pulled my pieces of the last exchange"
 
     def close(self) -> None:
         for r, base in enumerate(getattr(self, "bases", [])):
@@ -187,10 +203,19 @@ class PeerGather:
                     self.sides[k % len(self.sides)].cuda_stream))
 
     def finish(self) -> None:
-        """Current stream: wait for the pulls, then for every peer to have finished pulling from this rank."""
+        """Current stream: wait for this rank's pulls.  That the peers have finished pulling FROM this rank is only
+        needed before this rank's weights are rewritten: the all-reduce that says so is started here and waited
+        for by `before_step`, so the end of a step does not wait for the slowest rank."""
         for side in self.sides:
             torch.cuda.current_stream().wait_stream(side)
-        dist.all_reduce(self.flag, group=self.group)
+        self.pulled = dist.all_reduce(self.flag, group=self.group, async_op=True)
+
+    def before_step(self) -> None:
+        """Current stream: the step about to be enqueued rewrites this rank's pieces; every peer must have pulled
+        the previous ones."""
+        if self.pulled is not None:
+            self.pulled.wait()
+            self.pulled = None
 
 
 class ShardedStepper:
@@ -199,10 +224,11 @@ class ShardedStepper:
     bucket b travels over NVLink while bucket b+1 is being stepped.  `gather_mode`: "nccl" (in-place
     all_gather_into_tensor per bucket) or "peer" (copy-engine pulls over CUDA IPC mappings, see PeerGather)."""
 
-    def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer, gather_mode: str = "nccl"):
+    def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer, gather_mode: str = "nccl",
+                 group=None):
         if gather_mode not in ("nccl", "peer", "auto"):
             raise ValueError("gather_mode must be 'nccl', 'peer' or 'auto'")
-        self.sharded = sharded
+        self.sharded, self.group = sharded, group
         self.opts = []
         for b in range(sharded.n_buckets):
             ps = [params_by_index[i] for i in sharded.owned_in_bucket(b)]
@@ -210,25 +236,24 @@ class ShardedStepper:
         self.peer = None
         self.gather_mode = "nccl"
         if gather_mode != "nccl" and sharded.world_size > 1:
-            # "auto": use the copy-engine exchange when every rank could map every peer, else NCCL (all ranks agree)
-            err = None
-            try:
-                self.peer = PeerGather(sharded)
-            except Exception as e:      # noqa: BLE001 - any mapping failure means: not available here
-                err = e
-            ok = torch.tensor([0.0 if err else 1.0], device=sharded.flat.device)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            # "auto": use the copy-engine exchange when every rank could map every peer, else NCCL (all ranks agree:
+            # every rank runs the same two collectives whatever failed locally)
+            self.peer = PeerGather(sharded, group=group)
+            ok = torch.tensor([0.0 if self.peer.error else 1.0], device=sharded.flat.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
             if ok.item() == 1.0:
                 self.gather_mode = "peer"
             else:
-                if self.peer is not None:
-                    self.peer.close()
-                    self.peer = None
+                err = self.peer.error
+                self.peer.close()
+                self.peer = None
                 if gather_mode == "peer":
                     raise RuntimeError(f"peer mapping of the parameter buffers failed on some rank: {err}")
 
     def step(self, gather: bool = True):
         works = []
+        if self.peer is not None:
+            self.peer.before_step()
         for b, opt in enumerate(self.opts):
             if opt is not None:
                 opt.step()
@@ -236,7 +261,7 @@ class ShardedStepper:
                 if self.peer is not None:
                     self.peer.pull_bucket(b)
                 else:
-                    works.append(self.sharded.all_gather_bucket(b, async_op=True))
+                    works.append(self.sharded.all_gather_bucket(b, group=self.group, async_op=True))
         for w in works:
             w.wait()
         if gather and self.peer is not None:
@@ -270,11 +295,12 @@ class ShardedStepper:
         if self.sharded.world_size == 1:
             return
         if self.peer is not None:
+            self.peer.before_step()
             for b in range(self.sharded.n_buckets):
                 self.peer.pull_bucket(b)
             self.peer.finish()
         else:
-            self.sharded.all_gather()
+            self.sharded.all_gather(group=self.group)
 
     @property
     def last_step_launches(self) -> int:

@@ -87,6 +87,11 @@ def dequantize_tile16(q: torch.Tensor, absmax: torch.Tensor) -> torch.Tensor:
     qc = q.contiguous()
     rows, cols = qc.shape
     a = absmax.reshape(-1).to(torch.float32).contiguous()
+    need = math.ceil(rows / 16) * math.ceil(cols / 16)
+    if a.device != q.device:
+        raise RuntimeError(f"absmax is on {a.device}, the codes on {q.device}")
+    if a.numel() < need:
+        raise RuntimeError(f"absmax has {a.numel()} entries, {need} needed")
     out = torch.empty((rows, cols), device=q.device, dtype=torch.float32)
     with torch.cuda.device(q.device):
         _lib.check(lib.came_b200_dequantize_tile16(qc.data_ptr(), a.data_ptr(), out.data_ptr(), rows, cols, _stream(q)))

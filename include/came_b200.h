@@ -170,6 +170,15 @@ int came_b200_plan_set_hyper(came_plan_t* plan, const CameHyper* hypers, int n_g
  */
 int came_b200_plan_status(came_plan_t* plan, came_stream_t stream, int* status);
 
+/*
+ * Self-test of that bounded wait, without a step: enqueues a one-CTA kernel in which two warps wait, through the wait
+ * routine of the step kernels, on a barrier that nothing completes; the first has a limit of 4096 polls, the second the
+ * full limit.  device_words: three ints of device memory; after the stream has run they hold {1 (the status a timed-out
+ * wait records), 0, 0 (neither wait reported success; the second left through the abort flag the first raised)}.
+ * Nothing is left in flight and the context stays usable.  No counterpart in the reference.
+ */
+int came_b200_selftest_bounded_wait(int* device_words, came_stream_t stream);
+
 /* Number of kernel launches the last came_b200_step on this plan enqueued. */
 int came_b200_plan_last_launches(const came_plan_t* plan);
 
@@ -180,7 +189,7 @@ int came_b200_plan_last_launches(const came_plan_t* plan);
  * read_timing waits for the recorded events, adds their durations into ms[k] / launches[k]
  * (arrays of CAME_KERNEL_COUNT, zeroed by the callee) and forgets them.
  */
-#define CAME_KERNEL_COUNT 12
+#define CAME_KERNEL_COUNT 13
 int came_b200_plan_set_timing(came_plan_t* plan, int enable);
 int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches);
 const char* came_b200_kernel_name(int kernel);

@@ -80,3 +80,21 @@ def test_set_hyper_rejects_bad_records():
     bad = _lib.CameHyper()
     with pytest.raises(_lib.CameError):
         plan.set_hyper([bad, bad])      # clip_threshold 0
+
+
+def test_bounded_wait_runs_out_cleanly():
+    """A wait inside the kernels that never completes must end by itself: status word 1, both warps back, and the
+    context still usable afterwards (a normal step right after)."""
+    import came_b200
+    from came_b200 import _lib
+    lib = _lib.load()
+    words = torch.full((3,), 7, device="cuda", dtype=torch.int32)
+    _lib.check(lib.came_b200_selftest_bounded_wait(words.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert words.tolist() == [1, 0, 0]
+    p = torch.nn.Parameter(torch.ones(64, 64, device="cuda"))
+    p.grad = torch.ones(64, 64, device="cuda")
+    opt = came_b200.CAME8bit([p], lr=1e-3)
+    opt.step()
+    assert all(plan.status() == 0 for plan in opt._engine.plans.values())
+    assert bool((p.data < 1.0).all())

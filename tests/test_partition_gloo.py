@@ -115,3 +115,52 @@ def test_weighted_assignment_follows_the_weights():
         assign_owners([1, 2], 2, [1.0])
     sp = ShardedParams(SHAPES, torch.float32, "cpu", world_size=1, rank=0, buckets=3, bucket_weights=[1.0, 2.0, 1.0])
     assert sorted(i for b in range(3) for i in sp.owned_in_bucket(b)) == list(range(len(SHAPES)))
+
+
+def _fallback_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import came_b200.partition as part
+
+        real = part._lib.load()
+
+        class Lib:      # rank 0 "exports" a handle, rank 1 cannot: the ranks must still agree on the exchange mode
+            def __getattr__(self, name):
+                return getattr(real, name)
+
+            def came_b200_ipc_export(self, ptr, handle, offset):
+                return part._lib.OK if rank == 0 else part._lib.E_CUDA
+
+        part._lib.load = lambda: Lib()
+        sp = ShardedParams(SHAPES, torch.float32, "cpu", world, rank, buckets=2)
+
+        class Noop:
+            last_step_launches = 0
+
+            def __init__(self, idx):
+                self.idx = idx
+
+            def step(self):
+                for i in self.idx:
+                    sp.views[i].fill_(float(rank + 1))
+
+        st = ShardedStepper(sp, {i: i for i in sp.owned}, Noop, gather_mode="auto")
+        assert st.gather_mode == "nccl" and st.peer is None
+        st.step()
+        for v, o in zip(sp.views, sp.owners):
+            assert float(v.flatten()[0]) == float(o + 1)
+        with pytest.raises(RuntimeError):
+            ShardedStepper(sp, {i: i for i in sp.owned}, Noop, gather_mode="peer")
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_mode_falls_back_consistently_when_one_rank_cannot_export(tmp_path):
+    """`auto`: a rank whose export fails still joins every collective of the set-up, and all ranks end in the NCCL
+    (here: gloo) mode; `peer` raises on every rank."""
+    world = 2
+    mp.spawn(_fallback_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all(os.path.exists(os.path.join(str(tmp_path), f"ok{r}")) for r in range(world))

@@ -6,6 +6,8 @@ them the library keeps the 1-D step's block sums in a fixed device array of its 
 point through the C ABI next to the regular one (an optimizer class -> `came_b200_step`) on the same inputs, two
 steps in a row (the second call meets whatever the first left in the shared array), and expects identical bytes.
 
+The last case runs at the size limit (all 16 384 slots of the array).
+
 It lives in a file that pytest collects last, so that a failure here cannot hide the results of the other tests.
 """
 import ctypes as C
@@ -28,7 +30,7 @@ def _noalloc_step(lib, _lib, p, g, m, m_absmax, v, v_absmax, mode, flags, hyper)
 
 
 @pytest.mark.parametrize("cls_name,n,dtype", [("CAME8bitFull", 5000, torch.bfloat16), ("CAME8bitMemory", 70001, torch.float16),
-                                              ("CAMECUDA", 300, torch.float32)])
+                                              ("CAMECUDA", 300, torch.float32), ("CAME8bitFull", 1 << 22, torch.bfloat16)])
 def test_noalloc_matches_regular_entry_point_two_steps_in_a_row(cls_name, n, dtype):
     import came_b200
     from came_b200 import _lib
