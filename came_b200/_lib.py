@@ -25,7 +25,7 @@ F_UPDATE_F16 = 1 << 7
 F_RSQRT_CLAMP = 1 << 8
 
 MAX_GROUPS = 64
-KERNEL_COUNT = 13
+KERNEL_COUNT = 20
 NOALLOC_MAX_ELEMS = 1 << 22
 OK, E_INVALID, E_WORKSPACE, E_CUDA, E_UNSUPPORTED = 0, -1, -2, -3, -4
 
@@ -39,7 +39,7 @@ class CameTensorDesc(C.Structure):
         ("res_col", C.c_void_p), ("res_col_absmax", C.c_void_p),
         ("rows", C.c_int64), ("cols", C.c_int64),
         ("mode", C.c_int32), ("p_dtype", C.c_int32), ("g_dtype", C.c_int32), ("group", C.c_int32),
-        ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("flags", C.c_uint32), ("batch", C.c_uint32),
     ]
 
 

@@ -57,6 +57,7 @@ struct LaunchItem {
 };
 
 inline int elem_bytes(int dt) { return dt == CAME_DT_F32 ? 4 : 2; }
+inline bool is_nd(const CameTensorDesc& d) { return d.cols != 0 && d.batch > 1; }
 
 // vector-path eligibility of a tensor for each kernel family
 struct VecFlags {
@@ -69,7 +70,7 @@ struct VecFlags {
 
 VecFlags vec_flags(const CameTensorDesc& d) {
     VecFlags v{0, 0, 0, 0};
-    if (d.cols == 0) return v;
+    if (d.cols == 0 || is_nd(d)) return v;      // 1-D and N-D tensors have kernels of their own
     const bool c8 = d.cols % 8 == 0, c16 = d.cols % 16 == 0;
     // staged fast path of the momentum / apply passes: both or neither, as they share the tile geometry
     const bool all_aligned = aligned16(d.g) && aligned16(d.m) && aligned16(d.p);
@@ -101,6 +102,12 @@ Geometry geometry(const CameTensorDesc& d) {
         g.floats = align_up((size_t)g.nbR + 1, 4);
         return g;
     }
+    if (is_nd(d)) {      // nbR / nbC: blocks of the flattened row / column vectors; flat_chunks: flat blocks of 256 elements
+        g.nbR = (int)cdiv((int64_t)d.batch * g.R, QBLOCK);
+        g.nbC = (int)cdiv((int64_t)d.batch * g.C, QBLOCK);
+        g.flat_chunks = cdiv((int64_t)d.batch * g.R * g.C, QBLOCK);
+        return g;
+    }
     g.nbC = (int)cdiv(g.C, QBLOCK);
     g.tiles_r = (int)cdiv(g.R, K_TR);
     g.tiles_c = (int)cdiv(g.C, K_TC);
@@ -123,6 +130,14 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
     s.nbR = g.nbR;
     if (d.cols == 0) {
         s.spart = take((size_t)g.nbR + 1);      // block partials of sum u^2, then their sum
+    } else if (is_nd(d)) {
+        const size_t B = d.batch;
+        s.nbC = g.nbC;
+        s.vr = take(B * (size_t)g.R); s.vc = take(B * (size_t)g.C);
+        s.Rr = take(B * (size_t)g.R); s.Rc = take(B * (size_t)g.C);
+        s.rowblk = take(B); s.rowblk2 = take(B);      // per matrix: guarded mean of the fresh row vectors
+        s.scal = take(4);
+        s.spart = take((size_t)g.flat_chunks);
     } else {
         s.nbC = g.nbC;
         s.tiles_r = g.tiles_r; s.tiles_c = g.tiles_c;
@@ -172,6 +187,11 @@ int validate(const CameTensorDesc& d, int i) {
         return CAME_OK;
     }
     if (!d.sq_col || !d.res_row || !d.res_col) return fail(CAME_E_INVALID, "tensor %d: missing factored state", i);
+    if (d.batch > 1) {
+        if (d.mode == CAME_MODE_TILE8) return fail(CAME_E_INVALID, "tensor %d: the tile layout holds single matrices (batch %u)", i, d.batch);
+        if ((double)d.batch * (double)d.rows * (double)d.cols > 9.0e18) return fail(CAME_E_UNSUPPORTED, "tensor %d: too many elements", i);
+        if (cdiv((int64_t)d.batch * d.rows * d.cols, QBLOCK) > 0x7fffffffLL) return fail(CAME_E_UNSUPPORTED, "tensor %d: too many elements", i);
+    }
     if (quant && (!d.sq_col_absmax || !d.res_row_absmax || !d.res_col_absmax))
         return fail(CAME_E_INVALID, "tensor %d: missing factored absmax", i);
     return CAME_OK;
@@ -188,6 +208,10 @@ size_t count_work(const CameTensorDesc* descs, int n) {
         const Geometry g = geometry(descs[i]);
         if (descs[i].cols == 0) {
             w += 2 * (size_t)g.nbR + 1;      // partial, apply; one reduce CTA
+            continue;
+        }
+        if (is_nd(descs[i])) {      // two vector passes, two mean passes (one item per matrix), S, two element passes
+            w += 2 * (size_t)(g.nbR + g.nbC) + 2 * (size_t)descs[i].batch + 1 + 2 * (size_t)g.flat_chunks;
             continue;
         }
         w += 2 * (size_t)g.tiles_r * g.tiles_c;      // sq_partials, sumsq
@@ -375,17 +399,29 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     };
     const CameTensorDesc* D = descs;
     auto is1d = [&](int i) { return D[i].cols == 0; };
-    auto is2d = [&](int i) { return D[i].cols != 0; };
-    auto isflat = [&](int i) { return D[i].cols != 0 && D[i].mode == CAME_MODE_FLAT8; };
-    auto notflat = [&](int i) { return D[i].cols != 0 && D[i].mode != CAME_MODE_FLAT8; };
+    auto is2d = [&](int i) { return D[i].cols != 0 && !is_nd(D[i]); };
+    auto isnd = [&](int i) { return is_nd(D[i]); };
+    auto isflat = [&](int i) { return is2d(i) && D[i].mode == CAME_MODE_FLAT8; };
+    auto notflat = [&](int i) { return is2d(i) && D[i].mode != CAME_MODE_FLAT8; };
     auto nokey = [&](int) { return Key{0, 0, 0, 0}; };
     const auto& vf = plan->vflags;
 
     build(KID_NF_PARTIAL, is1d, [&](int i) { return Key{D[i].g_dtype, 0, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
     build(KID_NF_REDUCE, is1d, nokey, [&](int) { return (int64_t)1; });
     build(KID_NF_APPLY, is1d, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, 0}; }, [&](int i) { return (int64_t)geo[i].nbR; });
-    auto fusedA = [&](int i) { return D[i].cols != 0 && vf[i].k == 2; };
-    auto twopass = [&](int i) { return D[i].cols != 0 && vf[i].k != 2; };
+    // tensors of more than two dimensions
+    auto nvec = [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; };
+    auto nmat = [&](int i) { return (int64_t)D[i].batch; };
+    auto nblk = [&](int i) { return geo[i].flat_chunks; };
+    build(KID_ND_SQ, isnd, nokey, nvec);
+    build(KID_ND_MEAN, isnd, nokey, nmat);
+    build(KID_ND_SUMSQ, isnd, nokey, nblk);
+    build(KID_ND_S, isnd, nokey, [&](int) { return (int64_t)1; });
+    build(KID_ND_RES, isnd, nokey, nvec);
+    build(KID_ND_RESMEAN, isnd, nokey, nmat);
+    build(KID_ND_APPLY, isnd, nokey, nblk);
+    auto fusedA = [&](int i) { return is2d(i) && vf[i].k == 2; };
+    auto twopass = [&](int i) { return is2d(i) && vf[i].k != 2; };
     auto fused_code = [&](int i) {      // column groups per thread | row sets << 4 | ring slot KB << 8
         int groups, ng, rb, slot_kb;
         fused_sq_geometry(D[i].cols, elem_bytes(D[i].g_dtype), &groups, &ng, &rb, &slot_kb);
@@ -408,7 +444,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     std::vector<char> fused(n_tensors, 0);
     if (!g_disable_fast && fused_ma_enabled()) {
         for (int i = 0; i < n_tensors; ++i)
-            fused[i] = D[i].cols != 0 && D[i].mode == CAME_MODE_TILE8 && vf[i].p2 == 2 && vf[i].p3 == 2 && D[i].g_dtype == D[i].p_dtype;
+            fused[i] = is2d(i) && D[i].mode == CAME_MODE_TILE8 && vf[i].p2 == 2 && vf[i].p3 == 2 && D[i].g_dtype == D[i].p_dtype;
     }
     {
         const int grid = persistent_grid_limit();
@@ -574,6 +610,8 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
             e = launch_nonfactored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         else if (it.kernel == KID_SQ_PARTIALS && it.key.variant == 2)
             e = launch_fused_sq(it.key, a, wbase + it.work_off, it.n, st);
+        else if (it.kernel >= KID_ND_SQ && it.kernel <= KID_ND_APPLY)
+            e = launch_nd(it.kernel, a, wbase + it.work_off, it.n, st);
         else if (it.kernel == KID_MOMENT_APPLY)
             e = launch_fused_ma(it.key, a, wbase + it.work_off, it.n, wbase + it.work2_off, it.n2, sync, sync + plan->n_tensors,
                                 sync + 2 * plan->n_tensors + 2 * (fused_launches++ % 3), st);      // two list cursors per launch (at most 3)
@@ -686,7 +724,8 @@ int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches) {
 const char* came_b200_kernel_name(int kernel) {
     static const char* names[CAME_KERNEL_COUNT] = {
         "sq_partials", "sq_finalize", "sumsq", "s_finalize", "moment", "res_finalize",
-        "apply", "factors", "apply_flat", "nf_partial", "nf_apply", "nf_reduce", "moment_apply"};
+        "apply", "factors", "apply_flat", "nf_partial", "nf_apply", "nf_reduce", "nd_sq", "nd_mean", "nd_sumsq", "nd_s", "nd_res",
+        "nd_resmean", "nd_apply", "moment_apply"};
     return (kernel >= 0 && kernel < CAME_KERNEL_COUNT) ? names[kernel] : "?";
 }
 

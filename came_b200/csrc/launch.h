@@ -37,6 +37,13 @@ enum KernelId {
     KID_NF_PARTIAL,
     KID_NF_APPLY,
     KID_NF_REDUCE,
+    KID_ND_SQ,             // tensors of more than two dimensions (nd.cu)
+    KID_ND_MEAN,
+    KID_ND_SUMSQ,
+    KID_ND_S,
+    KID_ND_RES,
+    KID_ND_RESMEAN,
+    KID_ND_APPLY,
     KID_MOMENT_APPLY,      // momentum + residual finalize + apply of the tile layout as one kernel (fused_ma.cu)
     KID_COUNT
 };
@@ -62,6 +69,7 @@ bool fused_sq_eligible(int64_t cols, int elem_bytes);
 cudaError_t launch_nonfactored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                                cudaStream_t st);
 
+cudaError_t launch_nd(int kernel, const StepArgs& a, const Work* work, int n, cudaStream_t st);
 cudaError_t launch_selftest_bounded_wait(int* status, int* observed, cudaStream_t st);
 
 cudaError_t launch_quantize_blockwise(const float* src, void* q, float* absmax, int64_t n, bool is_signed,

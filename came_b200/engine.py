@@ -7,6 +7,7 @@ This is the replacement of the reference's extension shim (came_pytorch/came_cud
 from __future__ import annotations
 
 import ctypes as C
+import math
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -92,16 +93,19 @@ class DevicePlan:
         self.addresses = tuple((e.p.data_ptr(), e.g.data_ptr()) for e in entries)
         descs = (CameTensorDesc * self.n)()
         for d, e in zip(descs, entries):
-            if e.p.dim() not in (1, 2):
-                raise NotImplementedError("came_b200 steps 1-D and 2-D tensors")
+            if e.p.dim() < 1:
+                raise NotImplementedError("came_b200 does not step 0-dimensional tensors")
             d.p, d.g = e.p.data_ptr(), e.g.data_ptr()
             d.m, d.m_absmax = _ptr(e.m), _ptr(e.m_absmax)
             d.sq_row, d.sq_row_absmax = _ptr(e.sq_row), _ptr(e.sq_row_absmax)
             d.sq_col, d.sq_col_absmax = _ptr(e.sq_col), _ptr(e.sq_col_absmax)
             d.res_row, d.res_row_absmax = _ptr(e.res_row), _ptr(e.res_row_absmax)
             d.res_col, d.res_col_absmax = _ptr(e.res_col), _ptr(e.res_col_absmax)
-            d.rows = e.p.shape[0]
-            d.cols = e.p.shape[1] if e.p.dim() == 2 else 0
+            if e.p.dim() == 1:
+                d.rows, d.cols, d.batch = e.p.shape[0], 0, 0
+            else:      # more than two dimensions: a batch of [shape[-2], shape[-1]] matrices
+                d.rows, d.cols = e.p.shape[-2], e.p.shape[-1]
+                d.batch = math.prod(e.p.shape[:-2]) if e.p.dim() > 2 else 0
             d.mode, d.flags, d.group = e.mode, e.flags, e.group
             d.p_dtype, d.g_dtype = dtype_code(e.p.dtype), dtype_code(e.g.dtype)
         nbytes = self.lib.came_b200_workspace_bytes(descs, self.n)

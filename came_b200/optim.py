@@ -37,6 +37,9 @@ _FLAGS_CUDAFP_1D = _lib.F_RSQRT_CLAMP | _lib.F_WD_ADD2
 _FLAGS_TILE8 = _lib.F_SQ_FIX | _lib.F_RESROW_FIX | _lib.F_WD_MUL2
 _FLAGS_FLAT8_2D = _lib.F_SQ_FIX | _lib.F_RESROW_FIX | _lib.F_RESCOL_CLAMP
 _FLAGS_FLAT8_1D = _lib.F_RSQRT_CLAMP
+# tensors of more than two dimensions take the classes' generic torch paths in the reference (1e-30 clamps, two roundings
+# of p, Python scalars): CAMECUDA.py:275-326, CAME8bitFull.py:1006-1075
+_FLAGS_ND_GENERIC = _lib.F_SQ_CLAMP | _lib.F_RESROW_CLAMP | _lib.F_RESCOL_CLAMP | _lib.F_WD_ADD2
 
 _SCRATCH_KEYS = frozenset({
     # keys the reference keeps in its state dicts for kernel scratch; accepted on load, never produced
@@ -106,11 +109,13 @@ def init_state_flat(state: dict, p: torch.Tensor) -> None:
     factored = p.dim() >= 2
     state["factored"] = factored
     if factored:
-        rows, cols = p.shape
-        state["factored_row_q"] = torch.zeros((2, rows), device=dev, dtype=torch.uint8)
-        state["factored_row_absmax"] = torch.ones((2, _num_blocks(rows)), device=dev, dtype=torch.float32)
-        state["factored_col_q"] = torch.zeros((2, cols), device=dev, dtype=torch.uint8)
-        state["factored_col_absmax"] = torch.ones((2, _num_blocks(cols)), device=dev, dtype=torch.float32)
+        # CAME8bitFull.py:762-783: the vectors of an N-D tensor keep its leading dimensions; one absmax per 256 of their
+        # flattened entries
+        row_shape, col_shape = tuple(p.shape[:-1]), tuple(p.shape[:-2]) + tuple(p.shape[-1:])
+        state["factored_row_q"] = torch.zeros((2, *row_shape), device=dev, dtype=torch.uint8)
+        state["factored_row_absmax"] = torch.ones((2, _num_blocks(math.prod(row_shape))), device=dev, dtype=torch.float32)
+        state["factored_col_q"] = torch.zeros((2, *col_shape), device=dev, dtype=torch.uint8)
+        state["factored_col_absmax"] = torch.ones((2, _num_blocks(math.prod(col_shape))), device=dev, dtype=torch.float32)
         bind_flat_views(state)
         state["_cuda_factored_fastpath"] = True
         state["_cuda_factored_nd_ext_path"] = False
@@ -132,11 +137,11 @@ def init_state_fp(state: dict, p: torch.Tensor, *, mode_tag) -> None:
         state["factored"] = factored
     state["exp_avg"] = torch.zeros(shape, device=dev, dtype=torch.float32)
     if factored:
-        rows, cols = shape
-        state["exp_avg_sq_row"] = torch.zeros((rows,), device=dev, dtype=torch.float32)
-        state["exp_avg_sq_col"] = torch.zeros((cols,), device=dev, dtype=torch.float32)
-        state["exp_avg_res_row"] = torch.zeros((rows,), device=dev, dtype=torch.float32)
-        state["exp_avg_res_col"] = torch.zeros((cols,), device=dev, dtype=torch.float32)
+        row_shape, col_shape = shape[:-1], shape[:-2] + shape[-1:]      # CAMECUDA.py:93-98
+        state["exp_avg_sq_row"] = torch.zeros(row_shape, device=dev, dtype=torch.float32)
+        state["exp_avg_sq_col"] = torch.zeros(col_shape, device=dev, dtype=torch.float32)
+        state["exp_avg_res_row"] = torch.zeros(row_shape, device=dev, dtype=torch.float32)
+        state["exp_avg_res_col"] = torch.zeros(col_shape, device=dev, dtype=torch.float32)
     else:
         state["exp_avg_sq"] = torch.zeros(shape, device=dev, dtype=torch.float32)
     if mode_tag is not None:
@@ -203,7 +208,7 @@ class _CameB200Optimizer(torch.optim.Optimizer):
             g_data = g_data.contiguous()
             keep.append(g_data)
         e = Entry(p=p_data, g=g_data, mode=0, flags=flags, group=group_index, keep=keep)
-        factored = p.dim() == 2
+        factored = p.dim() >= 2
         if layout == "fp":
             e.mode = _lib.MODE_FP32
             e.m = state["exp_avg"]
@@ -243,10 +248,6 @@ class _CameB200Optimizer(torch.optim.Optimizer):
                     raise RuntimeError(
                         "came_b200 steps CUDA tensors only (there is no CPU fallback); "
                         f"got a parameter on {p.device}")
-                if p.dim() > 2:
-                    raise NotImplementedError(
-                        "came_b200 does not step tensors with more than 2 dimensions yet "
-                        f"(got shape {tuple(p.shape)})")
                 if p.dim() == 0:
                     raise NotImplementedError("came_b200 does not step 0-dimensional parameters")
                 layout, flags, variant = self._route(p, grad, group)
@@ -406,6 +407,8 @@ class CAMECUDA(_CameB200Optimizer):
     def _route(self, p, grad, group):
         if p.dim() == 2:
             return "fp", _FLAGS_CUDAFP_2D, 0       # came_kernels.cu:5250-5413
+        if p.dim() > 2:
+            return "fp", _FLAGS_ND_GENERIC, 1      # CAMECUDA.py:275-326 (generic torch branch)
         return "fp", _FLAGS_CUDAFP_1D, 1           # CAMECUDA.py:247-273 (torch ops, Python scalars)
 
 
@@ -440,6 +443,8 @@ class CAME8bitFull(_CameB200Optimizer):
     def _flat_route(self, p):
         if p.dim() == 2:
             return "flat", _FLAGS_FLAT8_2D, 0
+        if p.dim() > 2:
+            return "flat", _FLAGS_ND_GENERIC, 1    # CAME8bitFull.py:1006-1075 (dequantise, torch ops, requantise)
         flags = _FLAGS_FLAT8_1D | (_lib.F_UPDATE_F16 if self.cuda_nonfactored_use_fp16_update else 0)
         return "flat", flags, 0
 
@@ -459,8 +464,8 @@ class CAME8bitMemory(CAME8bitFull):
                          cuda_nonfactored_use_fp16_update=False)
 
     def _route(self, p, grad, group):
-        if p.dim() == 2:
-            return "flat", _FLAGS_FLAT8_2D, 0
+        if p.dim() >= 2:
+            return self._flat_route(p)
         return "flat", _FLAGS_FLAT8_1D | _lib.F_UPDATE_F16, 0
 
 

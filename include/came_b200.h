@@ -79,7 +79,11 @@ typedef struct CameTensorDesc {
     int32_t g_dtype;
     int32_t group;        /* index into the hyper-parameter array given to step   */
     uint32_t flags;       /* CAME_F_*                                             */
-    uint32_t reserved;
+    uint32_t batch;       /* 0 or 1: one [rows, cols] matrix.  B > 1: a tensor of more than two dimensions seen as   */
+                          /* B contiguous [rows, cols] matrices with one RMS clip over the whole tensor; p, g, m    */
+                          /* hold B*rows*cols elements, the row / column vectors B*rows / B*cols entries, quantised */
+                          /* in blocks of 256 over those flattened entries (CAME8bitFull.py:1006-1075; modes FP32   */
+                          /* and FLAT8 only)                                                                        */
 } CameTensorDesc;
 
 /*
@@ -189,7 +193,7 @@ int came_b200_plan_last_launches(const came_plan_t* plan);
  * read_timing waits for the recorded events, adds their durations into ms[k] / launches[k]
  * (arrays of CAME_KERNEL_COUNT, zeroed by the callee) and forgets them.
  */
-#define CAME_KERNEL_COUNT 13
+#define CAME_KERNEL_COUNT 20
 int came_b200_plan_set_timing(came_plan_t* plan, int enable);
 int came_b200_plan_read_timing(came_plan_t* plan, float* ms, int* launches);
 const char* came_b200_kernel_name(int kernel);

@@ -160,13 +160,13 @@ def init_state(p: torch.Tensor, sem: Semantics) -> dict:
         # CAME.py:97-112, CAMECUDA.py:83-100
         st["exp_avg"] = torch.zeros(shape, dtype=F32)
         if factored:
-            R, C = shape
-            for k, n in (("exp_avg_sq_row", R), ("exp_avg_sq_col", C), ("exp_avg_res_row", R), ("exp_avg_res_col", C)):
+            rs, cs = shape[:-1], shape[:-2] + shape[-1:]      # CAMECUDA.py:93-98: row / column state shapes of an N-D tensor
+            for k, n in (("exp_avg_sq_row", rs), ("exp_avg_sq_col", cs), ("exp_avg_res_row", rs), ("exp_avg_res_col", cs)):
                 st[k] = torch.zeros(n, dtype=F32)
         else:
             st["exp_avg_sq"] = torch.zeros(shape, dtype=F32)
         return st
-    if sem.m_layout == "tile" and factored:
+    if sem.m_layout == "tile" and factored and p.dim() == 2:
         # came8bit2d_state.py:33-55: tile absmax starts at ZERO, vector absmax at ONE
         R, C = shape
         st["exp_avg_q"] = torch.zeros(shape, dtype=torch.int8)
@@ -176,10 +176,12 @@ def init_state(p: torch.Tensor, sem: Semantics) -> dict:
         st["exp_avg_q"] = torch.zeros(shape, dtype=torch.int8)
         st["exp_avg_absmax"] = torch.ones(num_blocks(p.numel()), dtype=F32)
     if factored:
-        R, C = shape
-        for k, n in (("exp_avg_sq_row", R), ("exp_avg_sq_col", C), ("exp_avg_res_row", R), ("exp_avg_res_col", C)):
+        # CAME8bitFull.py:762-783: the vectors of an N-D tensor keep the leading dimensions and are quantised in
+        # blocks of 256 over their flattened entries (a block may straddle matrices)
+        rs, cs = shape[:-1], shape[:-2] + shape[-1:]
+        for k, n in (("exp_avg_sq_row", rs), ("exp_avg_sq_col", cs), ("exp_avg_res_row", rs), ("exp_avg_res_col", cs)):
             st[k + "_q"] = torch.zeros(n, dtype=torch.uint8)
-            st[k + "_absmax"] = torch.ones(num_blocks(n), dtype=F32)
+            st[k + "_absmax"] = torch.ones(num_blocks(math.prod(n)), dtype=F32)
     else:
         st["exp_avg_sq_q"] = torch.zeros(shape, dtype=torch.uint8)
         st["exp_avg_sq_absmax"] = torch.ones(num_blocks(p.numel()), dtype=F32)
@@ -209,14 +211,15 @@ def _ema(old: torch.Tensor, new: torch.Tensor, beta: float, sem: Semantics) -> t
 
 
 def _factor_row(v: torch.Tensor, guard: str) -> torch.Tensor:
-    n = v.numel()
+    """Row factor; the mean runs over the rows of one matrix (the last dimension of the row state)."""
+    n = v.shape[-1]
     if guard == "none":        # CAME.py:61-66
-        return (v / v.mean()).rsqrt()
-    if guard == "clamp_py":    # CAMECUDA.py:67-69: only the mean is clamped in Python
-        return (v / v.mean().clamp_min(1e-30)).rsqrt()
-    mean = v.sum() / n
+        return (v / v.mean(dim=-1, keepdim=True)).rsqrt()
+    if guard == "clamp_py":    # CAMECUDA.py:67-69, CAME8bitFull.py:124-126: only the mean is clamped in Python
+        return (v / v.mean(dim=-1, keepdim=True).clamp_min(1e-30)).rsqrt()
+    mean = v.sum(dim=-1, keepdim=True) / n
     if guard == "fix":         # came_kernels.cu:319-320, 330
-        mean = mean if float(mean) > 0.0 else _f(1.0)
+        mean = torch.where(mean > 0, mean, torch.ones_like(mean))
         return (v / mean).rsqrt()
     if guard == "clamp":       # came_kernels.cu:591-592
         mean = torch.clamp_min(mean, 1e-30)
@@ -272,14 +275,16 @@ def _clip(u0: torch.Tensor, hp: Hyper, sem: Semantics) -> torch.Tensor:
 # ----------------------------------------------------------------------------------------------
 
 def step_factored(p: torch.Tensor, g: torch.Tensor, st: dict, hp: Hyper, sem: Semantics) -> torch.Tensor:
-    """One CAME step on a 2-D parameter; mutates `st`, returns the new parameter (dtype of p)."""
-    R, C = p.shape
+    """One CAME step on a factored parameter; mutates `st`, returns the new parameter (dtype of p).  A tensor of more
+    than two dimensions is a batch of [shape[-2], shape[-1]] matrices that share one RMS clip (over the whole tensor)
+    and whose state vectors are quantised over their flattened entries (CAME.py:117-172, CAME8bitFull.py:1006-1075)."""
+    R, C = p.shape[-2], p.shape[-1]
     gf = g.to(F32)
 
     # factored second moment (CAME.py:117-127; came_kernels.cu:61-96, 198-243, 298-333, 524-593)
     sq = gf * gf + _f(hp.eps0)
-    a = sq.sum(dim=1) / C
-    b = sq.sum(dim=0) / R
+    a = sq.sum(dim=-1) / C
+    b = sq.sum(dim=-2) / R
     vr = _ema(_load_vec(st, "exp_avg_sq_row", sem), a, hp.beta2, sem)
     vc = _ema(_load_vec(st, "exp_avg_sq_col", sem), b, hp.beta2, sem)
     r = _factor_row(vr, sem.guard_sq)                      # from the fresh fp32 values, not the codes
@@ -289,9 +294,9 @@ def step_factored(p: torch.Tensor, g: torch.Tensor, st: dict, hp: Hyper, sem: Se
 
     # update, RMS clip, momentum (CAME.py:129-145; came_kernels.cu:596-619, 2619-2627, 2246-2342)
     if sem.factor_order == "g_r_c":
-        u0 = (gf * r[:, None]) * c[None, :]
+        u0 = (gf * r[..., :, None]) * c[..., None, :]
     else:
-        u0 = (r[:, None] * c[None, :]) * gf
+        u0 = (r[..., :, None] * c[..., None, :]) * gf
     u = u0 / _clip(u0, hp, sem)
     if sem.m_layout == "fp32":
         m_old = st["exp_avg"]
@@ -304,8 +309,8 @@ def step_factored(p: torch.Tensor, g: torch.Tensor, st: dict, hp: Hyper, sem: Se
     # confidence / instability (CAME.py:147-162; came_kernels.cu:2631-2676, 2685-2779, 1124-1156, 1246-1287)
     diff = u - m
     res = diff * diff + _f(hp.eps1)
-    rho = res.sum(dim=1) / C
-    kap = res.sum(dim=0) / R
+    rho = res.sum(dim=-1) / C
+    kap = res.sum(dim=-2) / R
     Rr = _ema(_load_vec(st, "exp_avg_res_row", sem), rho, hp.beta3, sem)
     Rc = _ema(_load_vec(st, "exp_avg_res_col", sem), kap, hp.beta3, sem)
     rr = _factor_row(Rr, sem.guard_res_row)
@@ -326,9 +331,9 @@ def step_factored(p: torch.Tensor, g: torch.Tensor, st: dict, hp: Hyper, sem: Se
 
     # apply (CAME.py:160-172; came_kernels.cu:3332-3366, 2487-2511)
     if sem.factor_order == "g_r_c":
-        upd = (m_used * rr[:, None]) * rc[None, :]
+        upd = (m_used * rr[..., :, None]) * rc[..., None, :]
     else:
-        upd = (rr[:, None] * rc[None, :]) * m_used
+        upd = (rr[..., :, None] * rc[..., None, :]) * m_used
     return _apply(p, upd, hp, sem)
 
 
@@ -384,8 +389,10 @@ def step_nonfactored(p: torch.Tensor, g: torch.Tensor, st: dict, hp: Hyper, sem:
 
 
 def step(p: torch.Tensor, g: torch.Tensor, st: dict, hp: Hyper, sem: Semantics, **kw) -> torch.Tensor:
-    if p.dim() == 2:
+    if p.dim() >= 2:
+        if p.dim() > 2 and sem.m_layout == "tile":
+            raise NotImplementedError("the tile layout holds 2-D tensors only (CAME8bit.py:216-223)")
         return step_factored(p, g, st, hp, sem)
     if p.dim() == 1:
         return step_nonfactored(p, g, st, hp, sem, **kw)
-    raise NotImplementedError("oracle covers 1-D and 2-D tensors")
+    raise NotImplementedError("oracle covers tensors of one or more dimensions")

@@ -28,6 +28,10 @@ CASES = {
     "small_bf16": dict(shapes=[(64, 48), (1, 40), (40, 1), (300,)], dtype="bfloat16", steps=6, hyper=HYPER_LLAMA, seed=3),
     "nowd_f32": dict(shapes=[(32, 32), (256,)], dtype="float32", steps=4,
                      hyper=dict(HYPER_DEFAULT, weight_decay=0.0), seed=4),
+    # tensors of more than two dimensions: a conv-like weight with tiny matrices, a few larger ones (state-vector
+    # blocks of 256 straddle the matrices in both)
+    "nd_f32": dict(shapes=[(12, 5, 3, 3), (3, 40, 24)], dtype="float32", steps=5, hyper=HYPER_LLAMA, seed=8),
+    "nd_bf16": dict(shapes=[(4, 6, 3, 3), (2, 3, 17, 9)], dtype="bfloat16", steps=5, hyper=HYPER_LLAMA, seed=9),
 }
 CLASSES = ["CAME", "CAMECUDA", "CAME8bitFull", "CAME8bit", "CAME8bitMemory"]
 
