@@ -51,7 +51,7 @@ class CameHyper(C.Structure):
         ("eps0", C.c_float), ("eps1", C.c_float),
         ("clip_threshold", C.c_float),
         ("weight_decay", C.c_float), ("wd_lr", C.c_float), ("decay_mul", C.c_float),
-        ("reserved", C.c_float * 3),
+        ("grad_scale", C.c_float), ("reserved", C.c_float * 2),
     ]
 
 

@@ -300,9 +300,16 @@ static int check_hypers(const char* who, const came_plan* plan, const CameHyper*
 }
 
 // (the buffer is allocated when the plan is created: page-locking memory is not allowed while a stream is captured)
+// grad_scale == 0 (a zero-initialised record) means "no scaling"
+static void normalise_hypers(CameHyper* h, int n_groups) {
+    for (int i = 0; i < n_groups; ++i)
+        if (h[i].grad_scale == 0.0f) h[i].grad_scale = 1.0f;
+}
+
 static int stage_graph_hypers(const char* who, came_plan* plan, const CameHyper* hypers, int n_groups) {
     if (!plan->graph_hyp) return fail(CAME_E_CUDA, "%s: the plan has no page-locked hyper-parameter buffer", who);
     std::memcpy(plan->graph_hyp, hypers, (size_t)n_groups * sizeof(CameHyper));
+    normalise_hypers(plan->graph_hyp, n_groups);
     plan->graph_groups = n_groups;
     return CAME_OK;
 }
@@ -578,7 +585,9 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) { cap = cudaStreamCaptureStatusNone; cudaGetLastError(); }
     const bool capturing = cap == cudaStreamCaptureStatusActive;
-    const CameHyper* src = hypers;
+    std::vector<CameHyper> norm(hypers, hypers + n_groups);      // pageable source: read before the copy call returns
+    normalise_hypers(norm.data(), n_groups);
+    const CameHyper* src = norm.data();
     if (capturing) {
         rc = stage_graph_hypers("step", plan, hypers, n_groups);
         if (rc != CAME_OK) return rc;

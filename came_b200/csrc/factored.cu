@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(THREADS) k_sq_partials(StepArgs a, const Work*
     const int R = (int)d.rows, C = (int)d.cols;
     const int tr = w.tile / s.tiles_c, tc = w.tile - tr * s.tiles_c;
     const int row0 = tr * K_TR, col0 = tc * K_TC;
-    const float eps0 = a.hyp[d.group].eps0;
+    const float eps0 = a.hyp[d.group].eps0, gscale = a.hyp[d.group].grad_scale;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TG* __restrict__ g = reinterpret_cast<const TG*>(d.g);
 
@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(THREADS) k_sq_partials(StepArgs a, const Work*
                 load_run<8, VEC>(g, (int64_t)row * C + col, col, C, v);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
+                    v[e] *= gscale;
                     float q = fmaf(v[e], v[e], eps0);
                     if (!VEC && col + e >= C) q = 0.0f;
                     racc += q;
@@ -166,7 +167,11 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
     if (is_col) {
         const int parts = RES ? s.ptiles_r : s.sq_col_parts;
         colsum = column_partial_sum(s.colpart, parts, C, b, s_acc);
-        if (fused) tsum = column_partial_sum(s.tpart, parts, C, b, s_acc);
+        if (fused) {      // the fused first pass sums the raw gradient: the gradient scale enters here, squared
+            const float gs2 = h.grad_scale * h.grad_scale;
+            tsum = column_partial_sum(s.tpart, parts, C, b, s_acc) * gs2;
+            colsum *= gs2;
+        }
     }
     if (valid) {
         if (fused && !is_col) {
@@ -226,6 +231,7 @@ __global__ void __launch_bounds__(THREADS) k_sumsq(StepArgs a, const Work* __res
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TG* __restrict__ g = reinterpret_cast<const TG*>(d.g);
     const bool clamp = d.flags & CAME_F_SQ_CLAMP;
+    const float gscale = a.hyp[d.group].grad_scale;
     stage_factors<K_TR, K_TC>(s.vr, s.vc, s.rowblk, s.nbR, R, C, row0, col0, d.flags & CAME_F_SQ_FIX, clamp, clamp,
                               s_r, s_c, red);
     float cf[16];
@@ -248,7 +254,7 @@ __global__ void __launch_bounds__(THREADS) k_sumsq(StepArgs a, const Work* __res
                 load_run<8, VEC>(g, (int64_t)row * C + col, col, C, v);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float u = (v[e] * r) * cf[hh * 8 + e];   // masked elements: v = 0, cf = 0
+                    const float u = ((v[e] * gscale) * r) * cf[hh * 8 + e];   // masked elements: v = 0, cf = 0
                     acc = fmaf(u, u, acc);
                 }
             }
@@ -288,7 +294,7 @@ __global__ void __launch_bounds__(THREADS) k_s_finalize(StepArgs a, const Work* 
         const int R = (int)d.rows, C = (int)d.cols;
         const int hi = min(R + C, (w.tile + 1) * S_FIN_CHUNK);      // this CTA's chunk of the R + C entries
         for (int i = w.tile * S_FIN_CHUNK + threadIdx.x; i < hi; i += THREADS)
-            if (i < R) s.mfac[i] = row_factor(s.vr[i], mean, clamp) * inv_clip;
+            if (i < R) s.mfac[i] = row_factor(s.vr[i], mean, clamp) * inv_clip * a.hyp[d.group].grad_scale;   // g enters u through it
             else s.mfac_c[i - R] = col_factor(s.vc[i - R], clamp);
     }
 }
@@ -370,7 +376,7 @@ __global__ void __launch_bounds__(THREADS) k_moment(StepArgs a, const Work* __re
         float rs = 0.0f, amax = 0.0f;
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-            const float u = ((gv[e] * r) * cf[e]) * inv_clip;
+            const float u = (((gv[e] * h.grad_scale) * r) * cf[e]) * inv_clip;
             const float mn = m[e] * beta1 + om1 * u;
             const float df = u - mn;
             float res = fmaf(df, df, eps1);
@@ -562,7 +568,7 @@ __global__ void __launch_bounds__(THREADS) k_apply_flat(StepArgs a, const Work* 
             float mn = 0.0f;
             upd[e] = 0.0f;
             if (e < rem) {
-                const float u = ((gv[e] * fr[row]) * fc[col]) * inv_clip;
+                const float u = (((gv[e] * h.grad_scale) * fr[row]) * fc[col]) * inv_clip;
                 mn = (m[e] * sc) * beta1 + om1 * u;
                 upd[e] = (mn * frr[row]) * frc[col];
             }

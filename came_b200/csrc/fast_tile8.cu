@@ -495,7 +495,7 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
             mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
             float mean2 = warp_vector_sum(s.rowblk2, s.nbR, lane) / (float)R;
             mean2 = guard_mean(mean2, d.flags & CAME_F_RESROW_FIX, cr);
-            const float inv_clip = 1.0f / s.scal[1];
+            const float inv_clip = h.grad_scale / s.scal[1];      // the gradient scale enters u through the row factor
             for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS) {
                 const bool in = it.row0 + i < R;
                 sr[i] = in ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;

@@ -58,7 +58,7 @@ struct FaStrip {
     float* colpart;         // this strip's first row of column partials (row set 0)
     float* tpart;
     int C, row0, nrows, rb, nbatch, pad;
-    float eps0C, fC, beta2, om_beta2;
+    float eps0C, fC, beta2, om_beta2, gs2;      // gs2: grad_scale squared, applied to every sum of g^2
 };
 
 // Shared bookkeeping of one CTA.  Ring: full / empty per slot.  Strips alternate between two buffers (record +
@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
                 t.tpart = s.tpart + (int64_t)w.tile * RS * C;
                 t.C = C; t.row0 = row0; t.nrows = nrows; t.rb = rb; t.nbatch = nbatch;
                 t.eps0C = (float)C * h.eps0; t.fC = (float)C; t.beta2 = h.beta2; t.om_beta2 = h.om_beta2;
+                t.gs2 = h.grad_scale * h.grad_scale;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->ready[sb]);
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
                         const float* part = s_part + (gb & 1) * FA_WARPS + lane * ppr;
                         float sum = 0.0f;
                         for (int q = 0; q < ppr; ++q) sum += part[q];
-                        const float mean = (sum + t.eps0C) / t.fC;
+                        const float mean = (sum * t.gs2 + t.eps0C) / t.fC;
                         const float v = s_old[sb * K_TR + b * rb + lane] * t.beta2 + t.om_beta2 * mean;
                         t.vr[t.row0 + b * rb + lane] = v;
                         s_w[(gb & 1) * FA_RB + lane] = v > 0.0f ? 1.0f / v : 0.0f;

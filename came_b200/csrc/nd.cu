@@ -75,16 +75,16 @@ struct NdElem {
     float u, m;
 };
 __device__ __forceinline__ float nd_u0(const CameTensorDesc& d, const Scratch& s, const NdShape& sh, int64_t b, int64_t i, int64_t j,
-                                       int64_t f) {
+                                       int64_t f, float gscale) {
     const bool clamp = d.flags & CAME_F_SQ_CLAMP;
     const float r = row_factor(s.vr[b * sh.R + i], s.rowblk[b], clamp);
     const float c = col_factor(s.vc[b * sh.C + j], clamp);
-    return (nd_load(d.g, d.g_dtype, f) * r) * c;
+    return ((nd_load(d.g, d.g_dtype, f) * gscale) * r) * c;
 }
 __device__ __forceinline__ NdElem nd_moment(const CameTensorDesc& d, const Scratch& s, const CameHyper& h, const NdShape& sh,
                                             int64_t b, int64_t i, int64_t j, int64_t f, float inv_clip) {
     NdElem o;
-    o.u = nd_u0(d, s, sh, b, i, j, f) * inv_clip;
+    o.u = nd_u0(d, s, sh, b, i, j, f, h.grad_scale) * inv_clip;
     const float m_old = d.mode == CAME_MODE_FP32 ? reinterpret_cast<const float*>(d.m)[f]
                                                  : (float)reinterpret_cast<const int8_t*>(d.m)[f] * (d.m_absmax[f >> 8] / QMAX_I8);
     o.m = m_old * h.beta1 + h.om_beta1 * o.u;
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(THREADS) k_nd_vec(StepArgs a, const Work* __re
                 const float df = o.u - o.m;
                 x = fmaf(df, df, eps);
             } else {
-                const float g = nd_load(d.g, d.g_dtype, f);
+                const float g = nd_load(d.g, d.g_dtype, f) * h.grad_scale;
                 x = fmaf(g, g, eps);
             }
             acc += x;
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(THREADS) k_nd_sumsq(StepArgs a, const Work* __
     float u = 0.0f;
     if (f < sh.n) {
         const int64_t b = f / (sh.R * sh.C), rem = f - b * sh.R * sh.C, i = rem / sh.C, j = rem - i * sh.C;
-        u = nd_u0(d, s, sh, b, i, j, f);
+        u = nd_u0(d, s, sh, b, i, j, f, a.hyp[d.group].grad_scale);
     }
     const float t = block_sum(u * u, red);
     if (threadIdx.x == 0) s.spart[w.tile] = t;

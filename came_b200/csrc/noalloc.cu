@@ -68,7 +68,7 @@ __device__ __forceinline__ void noalloc_second_moment(const NoallocArgs& a, int 
                                                       float& v, float& u) {
     g = 0.0f; v = 0.0f; u = 0.0f;
     if (!valid) return;
-    g = load_any(a.g, a.g_dtype, idx);
+    g = load_any(a.g, a.g_dtype, idx) * a.h.grad_scale;
     const float old = a.quant ? (float)reinterpret_cast<const uint8_t*>(a.v)[idx] * (a.v_absmax[b] / QMAX_U8)
                               : reinterpret_cast<const float*>(a.v)[idx];
     v = old * a.h.beta2 + a.h.om_beta2 * fmaf(g, g, a.h.eps0);
@@ -174,6 +174,7 @@ extern "C" int came_b200_step_vector_noalloc(void* p, const void* g, void* m, fl
     NoallocArgs a{};
     a.p = p; a.g = g; a.m = m; a.m_absmax = m_absmax; a.v = v; a.v_absmax = v_absmax;
     a.n = n; a.quant = mode == CAME_MODE_FLAT8; a.p_dtype = p_dtype; a.g_dtype = g_dtype; a.flags = flags; a.h = *hyper;
+    if (a.h.grad_scale == 0.0f) a.h.grad_scale = 1.0f;      // a zero-initialised record means "no scaling"
     if (noalloc_partials_address(&a.partials) != cudaSuccess)
         return fail(CAME_E_CUDA, "step_vector_noalloc: cudaGetSymbolAddress failed");
     const int nblocks = (int)((n + QBLOCK - 1) / QBLOCK);

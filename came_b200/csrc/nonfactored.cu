@@ -18,7 +18,7 @@ __device__ __forceinline__ void nf_second_moment(const CameTensorDesc& d, const 
                                                  bool valid, float& g, float& v, float& u) {
     g = 0.0f; v = 0.0f; u = 0.0f;
     if (!valid) return;
-    g = to_f32(reinterpret_cast<const TG*>(d.g)[idx]);
+    g = to_f32(reinterpret_cast<const TG*>(d.g)[idx]) * h.grad_scale;
     float old;
     if (d.mode == CAME_MODE_FP32) {
         old = reinterpret_cast<const float*>(d.sq_row)[idx];

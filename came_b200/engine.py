@@ -56,7 +56,7 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def make_hyper(lr, betas, eps, clip_threshold, weight_decay, *, python_scalars: bool) -> CameHyper:
+def make_hyper(lr, betas, eps, clip_threshold, weight_decay, *, python_scalars: bool, grad_scale: float = 1.0) -> CameHyper:
     """fp32 hyper-parameters of one param_group.
 
     python_scalars=False: 1-beta, lr*wd and 1-lr*wd are formed in fp32 from the fp32-rounded inputs, as the
@@ -79,6 +79,7 @@ def make_hyper(lr, betas, eps, clip_threshold, weight_decay, *, python_scalars: 
     h.eps0, h.eps1 = f(eps[0]), f(eps[1])
     h.clip_threshold = f(clip_threshold)
     h.weight_decay = f(weight_decay)
+    h.grad_scale = f(grad_scale)      # every gradient is multiplied by it as the kernels read it
     return h
 
 

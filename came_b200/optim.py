@@ -231,13 +231,10 @@ class _CameB200Optimizer(torch.optim.Optimizer):
 
     # -- the step -----------------------------------------------------------------------------
     def _collect(self):
-        entries, hypers, copy_backs = [], [], []
+        entries, hypers, copy_backs = [], self._hypers(), []
         for gi, group in enumerate(self.param_groups):
             if gi >= _lib.MAX_GROUPS // 2:
                 raise RuntimeError(f"came_b200 supports at most {_lib.MAX_GROUPS // 2} param_groups")
-            hp = (group["lr"], group["betas"], group["eps"], group["clip_threshold"], group["weight_decay"])
-            hypers.append(make_hyper(*hp, python_scalars=False))
-            hypers.append(make_hyper(*hp, python_scalars=True))
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -262,11 +259,16 @@ class _CameB200Optimizer(torch.optim.Optimizer):
         return entries, hypers, copy_backs
 
     def _hypers(self):
+        """Two hyper-parameter records per param_group (kernel-style and Python-style scalars), re-read every step.
+        A group may carry `grad_scale` (default 1): its gradients are multiplied by it as the kernels read them, e.g.
+        the inverse of a loss scale, which saves the trainer's separate unscale pass over the gradients (the
+        reference, like torch's other optimizers, expects unscaled gradients)."""
         hypers = []
         for group in self.param_groups:
             hp = (group["lr"], group["betas"], group["eps"], group["clip_threshold"], group["weight_decay"])
-            hypers.append(make_hyper(*hp, python_scalars=False))
-            hypers.append(make_hyper(*hp, python_scalars=True))
+            gs = float(group.get("grad_scale", 1.0))
+            hypers.append(make_hyper(*hp, python_scalars=False, grad_scale=gs))
+            hypers.append(make_hyper(*hp, python_scalars=True, grad_scale=gs))
         return hypers
 
     def _signature(self):

@@ -101,7 +101,9 @@ typedef struct CameHyper {
     float weight_decay;                 /* 0 disables decay                             */
     float wd_lr;                        /* weight_decay * lr                            */
     float decay_mul;                    /* 1 - lr * weight_decay (CAME_F_WD_MUL2)       */
-    float reserved[3];
+    float grad_scale;                   /* every gradient is multiplied by this as it is read (the inverse of a loss  */
+                                        /* scale, say: saves the trainer's separate unscale pass over g); 0 means 1   */
+    float reserved[2];
 } CameHyper;
 
 typedef struct came_plan came_plan_t;

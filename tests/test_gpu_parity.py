@@ -324,3 +324,43 @@ def test_sharded_stepper_checkpoint_round_trip():
     bad = dict(saved, owners=[1] * len(shapes))
     with pytest.raises(ValueError):
         st2.load_state_dict(bad)
+
+
+def test_grad_scale_is_applied_on_load():
+    """`grad_scale` of a param_group multiplies every gradient as the kernels read it.  A power of two commutes with
+    every rounding, so stepping 1024 * g with grad_scale = 1 / 1024 must leave exactly the bytes of stepping g; a
+    general scale is compared with the oracle fed the scaled gradients."""
+    import came_b200
+    from tests.parity_util import make_inputs, hyper_of, relerr
+    shapes = [(256, 512), (130, 4096), (300, 72), (33, 17), (2, 40, 24), (700,)]
+    for cls in (came_b200.CAME8bit, came_b200.CAME8bitFull, came_b200.CAMECUDA):
+        finals = []
+        for scaled in (False, True):
+            params0, grads = make_inputs(shapes, torch.bfloat16, 3, seed=61)
+            gp = [torch.nn.Parameter(p.cuda()) for p in params0]
+            opt = cls(gp, **H_LLAMA)
+            if scaled:
+                opt.param_groups[0]["grad_scale"] = 1.0 / 1024.0
+            for gs in grads:
+                for p, g in zip(gp, gs):
+                    p.grad = (g.float() * (1024.0 if scaled else 1.0)).bfloat16().cuda()
+                opt.step()
+            finals.append([p.data.clone() for p in gp] +
+                          [v.clone() for p in gp for k, v in sorted(opt.state[p].items()) if torch.is_tensor(v)])
+        for x, y in zip(*finals):
+            assert torch.equal(x, y), cls.__name__
+    # a scale that is not a power of two, against the oracle
+    s = 0.37
+    params0, grads = make_inputs(shapes[:4], torch.bfloat16, 3, seed=62)
+    gp = [torch.nn.Parameter(p.cuda()) for p in params0]
+    opt = came_b200.CAME8bit(gp, **H_LLAMA)
+    opt.param_groups[0]["grad_scale"] = s
+    cp = [p.clone() for p in params0]
+    sts = [orc.init_state(p, orc.TILE8) for p in cp]
+    for gs in grads:
+        for i, (p, g) in enumerate(zip(gp, gs)):
+            p.grad = g.cuda()
+            cp[i] = orc.step(cp[i], g.float() * s, sts[i], hyper_of(H_LLAMA), orc.TILE8)
+        opt.step()
+    for p, c in zip(gp, cp):
+        assert relerr(p.data.float().cpu(), c.float()) <= 1e-3
