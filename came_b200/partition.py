@@ -115,6 +115,28 @@ class ShardedParams:
         works = [self.all_gather_bucket(b, group=group, async_op=async_op) for b in range(self.n_buckets)]
         return works if async_op else None
 
+    def like_flat(self) -> tuple:
+        """A second flat buffer with the same layout (for gradients) and the per-tensor views into it."""
+        flat = torch.zeros_like(self.flat)
+        views = []
+        for v in self.views:
+            start = (v.data_ptr() - self.flat.data_ptr()) // self.flat.element_size()
+            views.append(flat[start:start + v.numel()].view(v.shape))
+        return flat, views
+
+    def reduce_scatter_bucket(self, flat: torch.Tensor, b: int, group=None):
+        """Sums bucket b of `flat` (a buffer laid out like the parameters, e.g. every rank's local gradients) over
+        the ranks; each rank receives the sum of its own piece, in place.  Backends without reduce-scatter (gloo)
+        all-reduce the bucket instead."""
+        if self.world_size == 1:
+            return
+        region = flat[self.bucket_off[b]:self.bucket_off[b + 1]]
+        mine = region[self.rank * self.piece_len[b]:(self.rank + 1) * self.piece_len[b]]
+        if dist.get_backend(group) == "nccl":
+            dist.reduce_scatter_tensor(mine, region, op=dist.ReduceOp.SUM, group=group)
+        else:
+            dist.all_reduce(region, op=dist.ReduceOp.SUM, group=group)
+
     def gathered_bytes_per_rank(self) -> int:
         """Bytes each rank receives from its peers in one full all-gather."""
         return (self.world_size - 1) * self.slice_len * self.flat.element_size()
@@ -305,3 +327,66 @@ class ShardedStepper:
     @property
     def last_step_launches(self) -> int:
         return sum(o.last_step_launches for o in self.opts if o is not None)
+
+
+class Zero1Step:
+    """The whole data-parallel optimizer sequence of one step under the ownership partition, bucket by bucket:
+    reduce-scatter of the gradients (each rank receives the summed gradients of the tensors it owns), step of the owned
+    tensors, all-gather of the updated weights -- optionally captured into ONE CUDA graph, so that a training step
+    replays it with a single launch.  The reference has no counterpart (it is single-GPU; its `prime_for_cuda_graph`,
+    came_pytorch/CAME8bit2D.py:52-72, covers the bare step of one process).
+
+    `grad_flat` / `grad_views` come from `ShardedParams.like_flat()`: every rank writes its local gradients of ALL
+    parameters there; the parameters of the optimizers must have their `.grad` set to the views of the tensors the rank
+    owns.  Gradients are summed; give the optimizers' param_groups `grad_scale = 1 / world_size` for the mean (the
+    scale is applied as the kernels read the gradients).  The exchange inside a captured sequence is the NCCL
+    all-gather (collectives are captured as graph nodes)."""
+
+    def __init__(self, stepper: "ShardedStepper", grad_flat: torch.Tensor, group=None):
+        self.stepper, self.sharded, self.grad_flat, self.group = stepper, stepper.sharded, grad_flat, group
+        self.graph = None
+
+    def run(self) -> None:
+        s = self.sharded
+        for b, opt in enumerate(self.stepper.opts):
+            s.reduce_scatter_bucket(self.grad_flat, b, group=self.group)
+            if opt is not None:
+                opt.step()
+            if s.world_size > 1:
+                s.all_gather_bucket(b, group=self.group)
+
+    def capture(self, warmup: int = 0) -> None:
+        """Captures `run()` on a side stream.  The optimizers' states must exist (`prime_for_cuda_graph()` or earlier
+        steps) and the gradient / parameter buffers must stay where they are.  `warmup` eager runs come first (they DO
+        step)."""
+        for opt in self.stepper.opts:
+            if opt is not None:
+                opt.prime_for_cuda_graph()
+        side = torch.cuda.Stream(device=self.sharded.flat.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self.run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.run()
+
+    def replay(self) -> None:
+        """One step: re-reads the hyper-parameters from the param_groups (learning-rate schedules need no re-capture)
+        and replays the captured sequence."""
+        if self.graph is None:
+            raise RuntimeError("capture() first")
+        # The captured upload reads the staged hyper-parameter records when the graph RUNS: they may only be rewritten
+        # once the previous replay has run.  Unchanged hyper-parameters need no rewrite and no wait.
+        import ctypes as C
+        staged = [bytes(C.string_at(C.byref(h), C.sizeof(h))) for opt in self.stepper.opts if opt is not None
+                  for h in opt._hypers()]
+        if staged != getattr(self, "_staged", None):
+            torch.cuda.current_stream().synchronize()
+            for opt in self.stepper.opts:
+                if opt is not None:
+                    opt.update_captured_hypers()
+            self._staged = staged
+        self.graph.replay()

@@ -164,3 +164,41 @@ def test_exchange_mode_falls_back_consistently_when_one_rank_cannot_export(tmp_p
     world = 2
     mp.spawn(_fallback_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all(os.path.exists(os.path.join(str(tmp_path), f"ok{r}")) for r in range(world))
+
+
+def _zero1_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from came_b200.partition import Zero1Step
+        sp = ShardedParams(SHAPES, torch.float32, "cpu", world, rank, buckets=2)
+        gflat, gviews = sp.like_flat()
+        assert gflat.shape == sp.flat.shape and all(g.shape == v.shape for g, v in zip(gviews, sp.views))
+        for i, g in enumerate(gviews):
+            g.fill_(float((rank + 1) * (i + 1)))          # every rank's local gradient of every tensor
+
+        class SumApplier:      # "optimizer": subtracts the (summed) gradient of the tensors it owns
+            last_step_launches = 0
+
+            def __init__(self, idx):
+                self.idx = idx
+
+            def step(self):
+                for i in self.idx:
+                    sp.views[i].sub_(gviews[i])
+
+        st = ShardedStepper(sp, {i: i for i in sp.owned}, SumApplier)
+        Zero1Step(st, gflat).run()
+        total = sum(r + 1 for r in range(world))
+        for i, v in enumerate(sp.views):
+            assert torch.all(v == -float(total * (i + 1))), i      # every rank holds every tensor's update
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_zero1_sequence_reduces_steps_and_gathers(tmp_path):
+    world = 2
+    mp.spawn(_zero1_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all(os.path.exists(os.path.join(str(tmp_path), f"ok{r}")) for r in range(world))
