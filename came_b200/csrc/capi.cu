@@ -456,6 +456,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     {
         const int grid = persistent_grid_limit();
         const size_t lag_a = (size_t)std::max(0, env_int("CAME_B200_MA_LAG", 5 * grid));
+        const bool reverse_a = env_int("CAME_B200_MA_REVERSE", 1) != 0;
         for (int dt = CAME_DT_F32; dt <= CAME_DT_BF16; ++dt) {
             LaunchItem it{};
             it.kernel = KID_MOMENT_APPLY;
@@ -466,7 +467,10 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
             size_t next = 0, emitted = 0;
             auto burst = [&](const Burst& b) {
                 const int64_t c = (int64_t)geo[b.tensor].ptiles_r * geo[b.tensor].ptiles_c;
-                for (int64_t k = 0; k < c; ++k) work.push_back(Work{b.tensor, (int32_t)(((uint32_t)MA_KIND_A << 28) | (uint32_t)k)});
+                // the tiles written last are the likeliest to be still in L2: the apply items of a tensor run through its
+                // tiles in the reverse order (CAME_B200_MA_REVERSE=0: same order as the momentum items)
+                for (int64_t k = 0; k < c; ++k)
+                    work.push_back(Work{b.tensor, (int32_t)(((uint32_t)MA_KIND_A << 28) | (uint32_t)(reverse_a ? c - 1 - k : k))});
             };
             for (int i = 0; i < n_tensors; ++i) {
                 if (!fused[i] || D[i].g_dtype != dt) continue;

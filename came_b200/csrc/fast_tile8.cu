@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(M_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
 
     for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
         const int buf = n & 1;
-        if (!wide_wait(&sh->ready[buf], (n >> 1) & 1, sh, a, lane)) return;
+        if (!wide_wait(&sh->ready[buf], (n >> 1) & 1, sh, a, lane)) { wide_drain(sh, STAGES); return; }
         const MomentItem& mi = s_item[buf];
         const int R = mi.R, C = mi.C, row0 = mi.row0, nbands = mi.nbands;
         const bool active = cl < mi.wcols;        // warps beyond a ragged tile width idle
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(M_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
 #pragma unroll 1
         for (int k = 0; k < nbands; ++k, ++q) {
             const int slot = q % STAGES;
-            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) return;      // the status word is set
+            if (!wide_wait_full(a, sh, slot, (q / STAGES) & 1, lane)) { wide_drain(sh, STAGES); return; }      // the status word is set
             if (!active) { wide_release(sh, slot, lane); continue; }
             const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(TG);
             const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;

@@ -22,13 +22,17 @@
 // are resident), so the waits cannot deadlock; they are bounded all the same (status word, abort flag).
 //
 // Measured on Llama-7B shapes: 9.9 ms against 10.7 ms for the three launches, 94 % of the copy bandwidth for the bytes
-// actually moved.  The codes are written with an evict-last L2 policy and every stream that is read once carries
-// evict-first; with the apply items this far behind, the codes are nevertheless re-read from DRAM (the separation the
-// dependency needs, times the bandwidth, exceeds what the L2 keeps).
+// actually moved.  L2: every stream that is read once carries an evict-first policy; the codes of the last quarter of a
+// tensor's momentum tiles are written evict-last and the apply items run through the tiles in reverse order, which
+// lets them find about 70 % of that quarter in L2 (1.2 GB of 6.7 GB of codes per step).  Protecting every tile does not
+// work: with the apply items as far behind as the dependency needs (40 us times the bandwidth), more protected lines
+// are alive than the L2 keeps, and they crowd out each other; measured, it is slower than protecting none.
 //
 // The arithmetic of every item is that of the three separate kernels, operation for operation: the results are
 // bit-identical to theirs.
 #include "wide.cuh"
+
+#include <cstdlib>
 
 namespace came {
 
@@ -51,6 +55,7 @@ struct MaItem {
     float* m_absmax;
     float* colpart;
     float om_beta1, dq_beta1;
+    int keep;             // the codes this item writes are marked evict-last in L2
     // A
     void* p;
     float lr, wd_lr, decay_mul;
@@ -202,11 +207,19 @@ extern "C" int came_b200_debug_ma_profile(unsigned long long* out, int reset) {
 #define MA_CLOCK() 0ll
 #endif
 
+// After a failed wait: give the bulk copies that may still be in flight a bounded chance to land before the warp
+// leaves (the CTA's shared memory must not be released under them).  Every warp that gives up calls this.
+__device__ __forceinline__ void ma_drain(MaShared* sh, int stages) {
+    for (int i = 0; i < stages; ++i)
+        for (uint32_t t = 0; t < (1u << 16); ++t)
+            if (mbar_try_wait(&sh->full[i], 0) || mbar_try_wait(&sh->full[i], 1)) break;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepArgs a, const Work* __restrict__ work, int n_items,
                                                                           int* __restrict__ mcount, int* __restrict__ fcount,
                                                                           int* __restrict__ next_item, const Work* __restrict__ fwork,
-                                                                          int n_fitems, int* __restrict__ next_fitem) {
+                                                                          int n_fitems, int* __restrict__ next_fitem, int keep_pct) {
     constexpr int STAGES = WideCfg<T>::STAGES, STAGE = WideCfg<T>::STAGE, ROW = WideCfg<T>::ROW;
     extern __shared__ __align__(128) unsigned char smem[];
     MaShared* sh = reinterpret_cast<MaShared*>(smem + STAGES * STAGE);
@@ -269,11 +282,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             if (ok && lane == 0) mbar_arrive(&sh->done[buf]);
         }
         // after a failed wait somewhere in the CTA: let the copies in flight land before shared memory is released
-        if (*reinterpret_cast<volatile int*>(&sh->abort)) {
-            for (int i = 0; i < STAGES; ++i)
-                for (uint32_t t = 0; t < (1u << 16); ++t)
-                    if (mbar_try_wait(&sh->full[i], 0) || mbar_try_wait(&sh->full[i], 1)) break;
-        }
+        if (*reinterpret_cast<volatile int*>(&sh->abort)) ma_drain(sh, STAGES);
         return;
     }
 
@@ -335,7 +344,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
         // What an item needs to know about its tensor, cached per kind (consecutive M items mostly share a tensor, and
         // so do consecutive A items): filling an entry is a chain of dependent global loads, done once per tensor.
         struct TensorInfo {
-            int tensor, R, C, ptiles_c;
+            int tensor, R, C, ptiles_c, ntiles;
             const unsigned char* a_base;      // g (M) or p (A)
             const unsigned char* m_base;
             const unsigned char* x_base;      // tile absmax
@@ -357,7 +366,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 const Scratch& s = a.scr[w.tensor];
                 const CameHyper& h = a.hyp[d.group];
                 t.tensor = w.tensor;
-                t.R = (int)d.rows; t.C = (int)d.cols; t.ptiles_c = s.ptiles_c;
+                t.R = (int)d.rows; t.C = (int)d.cols; t.ptiles_c = s.ptiles_c; t.ntiles = s.ptiles_r * s.ptiles_c;
                 t.a_base = reinterpret_cast<const unsigned char*>(kind == MA_KIND_M ? d.g : d.p);
                 t.m_base = reinterpret_cast<const unsigned char*>(d.m);
                 t.x_base = reinterpret_cast<const unsigned char*>(d.m_absmax);
@@ -403,6 +412,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 mi.m_absmax = reinterpret_cast<float*>(const_cast<unsigned char*>(t.x_base));
                 mi.colpart = t.colpart;
                 mi.om_beta1 = t.om_beta1; mi.dq_beta1 = t.dq_beta1;
+                mi.keep = (int64_t)tile * 100 >= (int64_t)t.ntiles * (100 - keep_pct);
                 mi.p = const_cast<unsigned char*>(t.a_base); mi.lr = t.lr; mi.wd_lr = t.wd_lr; mi.decay_mul = t.decay_mul;
                 mi.wd_mode = t.wd_mode;
                 // the record written above comes before the arrival (same thread); the factor vectors were written by
@@ -516,7 +526,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
     const int c8 = lane & 7, rsub = lane >> 3;
     const int cl = warp * 64 + c8 * 8;          // this lane's first column inside a tile
     const u64 magic = splat(ROUND_MAGIC);
-    const uint64_t keep_policy = l2_policy_evict_last();      // the new codes are read back by the tensor's A items
+    const uint64_t keep_last = l2_policy_evict_last(), keep_first = l2_policy_evict_first();
     int q = 0;            // position of the next band to consume in this CTA's band stream
     int n = 0;            // items this CTA has gone through
 
@@ -526,7 +536,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
     for (;; ++n) {
         const int buf = n & 1;
         const long long t_r0 = MA_CLOCK();
-        if (!ma_wait(&sh->ready[buf], (n >> 1) & 1, sh, a, lane)) return;
+        if (!ma_wait(&sh->ready[buf], (n >> 1) & 1, sh, a, lane)) { ma_drain(sh, STAGES); return; }
         const MaItem& mi = s_item[buf];
         const int kind = mi.kind;
         if (prof) { MA_PROF_ADD(0 + (kind & 3), MA_CLOCK() - t_r0); MA_PROF_ADD(4, 1); }      // 0..3: wait for a record of kind k
@@ -549,6 +559,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             }
             const u64 om2 = splat(mi.om_beta1);
             const float dq_beta1 = mi.dq_beta1;
+            const uint64_t keep_policy = mi.keep ? keep_last : keep_first;
             int8_t* mdst = mi.m + (int64_t)(row0 + rsub) * C + col;
             float* amax_dst = mi.m_absmax + (int64_t)(row0 >> 4) * tile_cols + (col >> 4);
             const int64_t band_bytes = (int64_t)W_BAND * C;
@@ -560,7 +571,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             for (int k = 0; k < nbands; ++k, ++q) {
                 const int slot = q % STAGES;
                 const long long t_f0 = MA_CLOCK();
-                if (!ma_wait(&sh->full[slot], (uint32_t)((q / STAGES) & 1), sh, a, lane)) return;
+                if (!ma_wait(&sh->full[slot], (uint32_t)((q / STAGES) & 1), sh, a, lane)) { ma_drain(sh, STAGES); return; }
                 if (prof) MA_PROF_ADD(6, MA_CLOCK() - t_f0);      // 6: M bands, wait for data
                 if (!active) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->empty[slot]); continue; }
                 const unsigned char* sg = smem + slot * STAGE + cl * (int)sizeof(T);
@@ -667,7 +678,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             for (int k = 0; k < nbands; ++k, ++q) {
                 const int slot = q % STAGES;
                 const long long t_f0 = MA_CLOCK();
-                if (!ma_wait(&sh->full[slot], (uint32_t)((q / STAGES) & 1), sh, a, lane)) return;
+                if (!ma_wait(&sh->full[slot], (uint32_t)((q / STAGES) & 1), sh, a, lane)) { ma_drain(sh, STAGES); return; }
                 if (prof) MA_PROF_ADD(7, MA_CLOCK() - t_f0);      // 7: A bands, wait for data
                 if (!active) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->empty[slot]); continue; }
                 const unsigned char* sp = smem + slot * STAGE + cl * (int)sizeof(T);
@@ -738,13 +749,16 @@ template <typename T> static constexpr size_t ma_smem() {
 template <typename T>
 static cudaError_t launch_ma(const StepArgs& a, const Work* work, int n, const Work* fwork, int nf, int* mcount, int* fcount,
                              int* next_item, cudaStream_t st) {
+    // CAME_B200_MA_KEEP_PCT: share of a tensor's momentum tiles (the last written) whose codes are marked evict-last
+    static const int keep_pct = [] { const char* e = getenv("CAME_B200_MA_KEEP_PCT"); return e ? atoi(e) : 25; }();
     const int sms = persistent_grid_limit();
     const size_t smem = ma_smem<T>();
     cudaError_t e = cudaFuncSetAttribute(k_moment_apply_tile8<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     StepArgs args = a;
     int* next_fitem = next_item + 1;
-    void* params[] = {&args, &work, &n, &mcount, &fcount, &next_item, &fwork, &nf, &next_fitem};
+    int keep = keep_pct;
+    void* params[] = {&args, &work, &n, &mcount, &fcount, &next_item, &fwork, &nf, &next_fitem, &keep};
     // cooperative launch: every CTA of the grid is resident at once (CTAs wait for items other CTAs finish)
     return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_moment_apply_tile8<T>), dim3(n < sms ? n : sms),
                                        dim3(MA_ALL_THREADS), params, smem, st);
