@@ -136,7 +136,7 @@ __device__ __forceinline__ void ma_finalize_block(const StepArgs& a, int tensor,
         for (int t0 = 0; t0 < parts; t0 += 32) {
             float x[32];
 #pragma unroll
-            for (int k = 0; k < 32; ++k) x[k] = (valid && t0 + k < parts) ? col[(int64_t)(t0 + k) * nvec] : 0.0f;
+            for (int k = 0; k < 32; ++k) x[k] = (valid && t0 + k < parts) ? __ldcg(col + (int64_t)(t0 + k) * nvec) : 0.0f;   // written by other SMs: past L1
             if (is_col) {
 #pragma unroll
                 for (int k = 0; k < 32; ++k) chain[k & 7] += x[k];
@@ -326,7 +326,9 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 // blocks + 1.
                 __threadfence();      // acquire side of the counter: the other finalizers' writes are visible
                 const CameTensorDesc& d = a.descs[wf.tensor];
-                float mean = warp_vector_sum(s.rowblk2, s.nbR, lane) / (float)d.rows;
+                float part = 0.0f;      // warp_vector_sum's order, with loads that bypass L1 (other SMs wrote the values)
+                for (int i = lane; i < s.nbR; i += 32) part += __ldcg(s.rowblk2 + i);
+                float mean = warp_sum(part) / (float)d.rows;
                 mean = guard_mean(mean, d.flags & CAME_F_RESROW_FIX, d.flags & CAME_F_RESROW_CLAMP);
                 if (lane == 0) s.scal[2] = mean;
                 __threadfence();
