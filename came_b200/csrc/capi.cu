@@ -78,7 +78,9 @@ VecFlags vec_flags(const CameTensorDesc& d) {
                       ((d.mode == CAME_MODE_TILE8 && d.cols % 64 == 0) ||
                        (d.mode == CAME_MODE_FLAT8 && d.cols % 256 == 0 && d.g_dtype == d.p_dtype));
     v.k = c8 && aligned16(d.g);
-    if (v.k && !g_disable_fast && !(d.flags & CAME_F_SQ_CLAMP) && fused_sq_eligible(d.cols, elem_bytes(d.g_dtype))) v.k = 2;
+    // (tensors with the 1e-30 clamps take the fused first pass too: its closed form for the clip sum holds whenever no
+    // clamp binds, which the finalize checks; if one does, the two-pass sum runs for that tensor)
+    if (v.k && !g_disable_fast && fused_sq_eligible(d.cols, elem_bytes(d.g_dtype))) v.k = 2;
     v.p2 = (c16 && aligned16(d.g) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.p3 = (c16 && aligned16(d.p) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.flat = c8 && aligned16(d.g) && aligned16(d.p) && (reinterpret_cast<uintptr_t>(d.m) & 7u) == 0;
@@ -160,6 +162,7 @@ size_t carve(const CameTensorDesc& d, const Geometry& g, float* base, Scratch* o
             s.res_eps_deferred = 1;
             s.mfac = take((size_t)g.R);
             s.mfac_c = take((size_t)g.C);
+            s.mfac_c2 = d.mode == CAME_MODE_FLAT8 ? take((size_t)g.C) : nullptr;
         }
         if (vec_flags(d).k == 2) {
             s.fused_a = 1;
@@ -233,7 +236,7 @@ Layout layout(const CameTensorDesc* descs, int n) {
     L.off_scr = off;   off = align_up(off + (size_t)n * sizeof(Scratch));
     L.off_hyp = off;   off = align_up(off + (size_t)MAX_GROUPS * sizeof(CameHyper));
     L.off_status = off; off = align_up(off + sizeof(int));
-    L.off_sync = off;  off = align_up(off + (2 * (size_t)n + 8) * sizeof(int));   // fused kernel: per-tensor item counters, list cursors
+    L.off_sync = off;  off = align_up(off + (2 * (size_t)n + 12) * sizeof(int));   // fused kernel: per-tensor item counters, list cursors
     L.n_work = count_work(descs, n);
     L.off_work = off;  off = align_up(off + L.n_work * sizeof(Work));
     L.off_float = off;
@@ -439,7 +442,9 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     build(KID_SQ_PARTIALS, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     build(KID_SQ_FINALIZE, is2d, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
-    build(KID_SUMSQ, twopass, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k}; },
+    // (also for fused-first-pass tensors that carry the clamps: those CTAs return at once unless a clamp binds)
+    auto needs_sumsq = [&](int i) { return twopass(i) || (fusedA(i) && (D[i].flags & CAME_F_SQ_CLAMP)); };
+    build(KID_SUMSQ, needs_sumsq, [&](int i) { return Key{D[i].g_dtype, 0, 0, vf[i].k >= 1 ? 1 : 0}; },
           [&](int i) { return (int64_t)geo[i].tiles_r * geo[i].tiles_c; });
     // one CTA per tensor for the clip scalar; tensors of the staged momentum pass get one CTA per 2048 entries of
     // their factor vectors (each CTA repeats the cheap scalar part)
@@ -451,16 +456,19 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     std::vector<char> fused(n_tensors, 0);
     if (!g_disable_fast && fused_ma_enabled()) {
         for (int i = 0; i < n_tensors; ++i)
-            fused[i] = is2d(i) && D[i].mode == CAME_MODE_TILE8 && vf[i].p2 == 2 && vf[i].p3 == 2 && D[i].g_dtype == D[i].p_dtype;
+            fused[i] = is2d(i) && D[i].g_dtype == D[i].p_dtype &&
+                       ((D[i].mode == CAME_MODE_TILE8 && vf[i].p2 == 2 && vf[i].p3 == 2) ||
+                        (D[i].mode == CAME_MODE_FLAT8 && vf[i].p2 == 2 && vf[i].flat == 2));
     }
     {
         const int grid = persistent_grid_limit();
         const size_t lag_a = (size_t)std::max(0, env_int("CAME_B200_MA_LAG", 5 * grid));
         const bool reverse_a = env_int("CAME_B200_MA_REVERSE", 1) != 0;
-        for (int dt = CAME_DT_F32; dt <= CAME_DT_BF16; ++dt) {
+        for (int dm = 0; dm < 6; ++dm) {
+            const int dt = CAME_DT_F32 + dm % 3, md = dm < 3 ? CAME_MODE_TILE8 : CAME_MODE_FLAT8;
             LaunchItem it{};
             it.kernel = KID_MOMENT_APPLY;
-            it.key = KernelKey{dt, dt, CAME_MODE_TILE8, 2};
+            it.key = KernelKey{dt, dt, md, 2};
             it.work_off = work.size();
             struct Burst { size_t release; int tensor; };
             std::vector<Burst> pend;      // apply bursts waiting for their place in the list
@@ -473,7 +481,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
                     work.push_back(Work{b.tensor, (int32_t)(((uint32_t)MA_KIND_A << 28) | (uint32_t)(reverse_a ? c - 1 - k : k))});
             };
             for (int i = 0; i < n_tensors; ++i) {
-                if (!fused[i] || D[i].g_dtype != dt) continue;
+                if (!fused[i] || D[i].g_dtype != dt || D[i].mode != md) continue;
                 const int64_t c = (int64_t)geo[i].ptiles_r * geo[i].ptiles_c;
                 for (int64_t k = 0; k < c; ++k) {
                     work.push_back(Work{i, (int32_t)(((uint32_t)MA_KIND_M << 28) | (uint32_t)k)});
@@ -486,7 +494,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
             it.n = (int)(work.size() - it.work_off);
             it.work2_off = work.size();
             for (int i = 0; i < n_tensors; ++i) {
-                if (!fused[i] || D[i].g_dtype != dt) continue;
+                if (!fused[i] || D[i].g_dtype != dt || D[i].mode != md) continue;
                 for (int k = 0; k < geo[i].nbR + geo[i].nbC; ++k) work.push_back(Work{i, k});
             }
             it.n2 = (int)(work.size() - it.work2_off);
@@ -519,7 +527,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
         build(KID_APPLY, in_notflat, [&](int i) { return Key{0, D[i].p_dtype, D[i].mode, vf[i].p3}; },
               [&](int i) { return (int64_t)geo[i].ptiles_r * geo[i].ptiles_c; });
         auto flat_generic = [&](int i) { return isflat(i) && vf[i].flat != 2 && wave[i] == w; };
-        auto flat_staged = [&](int i) { return isflat(i) && vf[i].flat == 2 && wave[i] == w; };
+        auto flat_staged = [&](int i) { return isflat(i) && vf[i].flat == 2 && wave[i] == w && !fused[i]; };
         build(KID_FACTORS, flat_generic, nokey, [&](int i) { return (int64_t)geo[i].nbR + geo[i].nbC; });
         build(KID_APPLY_FLAT, flat_generic, [&](int i) { return Key{D[i].g_dtype, D[i].p_dtype, 0, vf[i].flat}; },
               [&](int i) { return geo[i].flat_chunks; });
@@ -538,6 +546,8 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     if (e == cudaSuccess)
         e = cudaMemcpyAsync(plan->ws + L.off_scr, scr.data(), (size_t)n_tensors * sizeof(Scratch), cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) e = cudaMemsetAsync(plan->ws + L.off_status, 0, sizeof(int), st);
+    // the scratch starts at zero once (flags in it are reset by the kernels that use them)
+    if (e == cudaSuccess) e = cudaMemsetAsync(plan->ws + L.off_float, 0, L.total - L.off_float, st);
     if (e == cudaSuccess && !work.empty())
         e = cudaMemcpyAsync(plan->ws + L.off_work, work.data(), work.size() * sizeof(Work), cudaMemcpyHostToDevice, st);
     // the host vectors above die at return: wait for the copies
@@ -608,7 +618,7 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     const Work* wbase = reinterpret_cast<const Work*>(plan->ws + plan->L.off_work);
     int* sync = reinterpret_cast<int*>(plan->ws + plan->L.off_sync);
     if (plan->has_fused_ma) {      // the per-tensor item counters start every step at zero
-        e = cudaMemsetAsync(sync, 0, (2 * (size_t)plan->n_tensors + 8) * sizeof(int), st);
+        e = cudaMemsetAsync(sync, 0, (2 * (size_t)plan->n_tensors + 12) * sizeof(int), st);
         if (e != cudaSuccess) return fail(CAME_E_CUDA, "step: counter reset: %s", cudaGetErrorString(e));
     }
     int launches = 0, fused_launches = 0;
@@ -627,7 +637,7 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
             e = launch_nd(it.kernel, a, wbase + it.work_off, it.n, st);
         else if (it.kernel == KID_MOMENT_APPLY)
             e = launch_fused_ma(it.key, a, wbase + it.work_off, it.n, wbase + it.work2_off, it.n2, sync, sync + plan->n_tensors,
-                                sync + 2 * plan->n_tensors + 2 * (fused_launches++ % 3), st);      // two list cursors per launch (at most 3)
+                                sync + 2 * plan->n_tensors + 2 * (fused_launches++ % 6), st);      // two list cursors per launch (at most 6)
         else
             e = launch_factored(it.kernel, it.key, a, wbase + it.work_off, it.n, st);
         if (timing) {

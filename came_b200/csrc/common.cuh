@@ -51,6 +51,7 @@ struct Scratch {
     int32_t fa_rb;                // fused first pass: rows per staged batch
     float* mfac;                  // staged momentum pass: row factors r_i / clip [R]
     float* mfac_c;                // staged passes: column factors [C], 16-byte aligned (c_j; after the residual finalize C'_j)
+    float* mfac_c2;               // flat layout on the staged path: C'_j (c_j stays in mfac_c for the apply items), else nullptr
     int32_t sq_col_parts;         // column partial sets the first pass leaves (strips, or strips x 2 warp groups)
     int32_t res_eps_deferred;     // 1: the residual partials hold sums of (u-m)^2 only; eps1 is added per row / column
                                   //    by the finalize kernel (cols * eps1, rows * eps1)

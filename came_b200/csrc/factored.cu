@@ -197,6 +197,9 @@ __global__ void __launch_bounds__(THREADS) k_vec_finalize(StepArgs a, const Work
             fresh[idx] = v;
         }
     }
+    // The fused first pass gets the clip sum from a closed form that assumes r_i^2 = mean / v_row_i and c_j^2 = 1 / v_col_j,
+    // i.e. that none of the 1e-30 clamps binds.  Far outside this range one could: the two-pass sum then runs instead.
+    if (fused && (d.flags & CAME_F_SQ_CLAMP) && valid && !(v >= 1e-20f && v <= 1e8f)) s.scal[3] = 1.0f;
     if (quant) {
         const float bmax = fix_absmax(block_max(valid ? v : 0.0f, red));   // syncs: every old absmax read is done
         if (threadIdx.x == 0) absmax[b] = bmax;
@@ -225,6 +228,7 @@ __global__ void __launch_bounds__(THREADS) k_sumsq(StepArgs a, const Work* __res
     const Work w = work[blockIdx.x];
     const CameTensorDesc& d = a.descs[w.tensor];
     const Scratch& s = a.scr[w.tensor];
+    if (s.fused_a && s.scal[3] == 0.0f) return;      // the fused first pass's closed form stands: nothing to do
     const int R = (int)d.rows, C = (int)d.cols;
     const int tr = w.tile / s.tiles_c, tc = w.tile - tr * s.tiles_c;
     const int row0 = tr * K_TR, col0 = tc * K_TC;
@@ -272,7 +276,7 @@ __global__ void __launch_bounds__(THREADS) k_s_finalize(StepArgs a, const Work* 
     const CameTensorDesc& d = a.descs[w.tensor];
     const Scratch& s = a.scr[w.tensor];
     float S;
-    if (s.fused_a) {
+    if (s.fused_a && s.scal[3] == 0.0f) {
         float mean = block_vector_sum(s.rowblk, s.nbR, red) / (float)d.rows;
         mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, d.flags & CAME_F_SQ_CLAMP);
         S = mean * block_vector_sum(s.spart, s.nbC, red);

@@ -80,16 +80,22 @@ __global__ void __launch_bounds__(M_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
             const CameHyper& h = a.hyp[d.group];
             float* sr = s_r + buf * W_TR;
             float* sc = s_c + buf * W_TC;
-            const float* fr = s.mfac + it.row0;              // r_i / clip, prepared once per tensor by k_s_finalize
-            const float* fc = s.mfac_c + it.col0;            // c_j
-            for (int i = lane; i < W_TR; i += 32) sr[i] = (it.row0 + i < it.R) ? fr[i] : 0.0f;
-            for (int i = lane; i < it.wcols; i += 32) sc[i] = fc[i];
+            // The factor slices (r_i / clip and c_j, prepared once per tensor by k_s_finalize) come by bulk copies that
+            // complete on the record's `ready` barrier: a loop of dependent global loads in this warp takes as long as
+            // the item itself under load.  Rows past the end of the matrix receive whatever follows in the scratch (the
+            // copy is rounded up to 16 bytes); the computing warps never use them.
+            const uint32_t c_bytes = (uint32_t)it.wcols * sizeof(float);
+            const uint32_t r_bytes = (uint32_t)((min(W_TR, it.R - it.row0) + 3) & ~3) * sizeof(float);
             if (lane == 0) {
                 MomentItem& mi = s_item[buf];
                 mi.m = reinterpret_cast<int8_t*>(d.m); mi.m_absmax = d.m_absmax; mi.colpart = s.colpart;
                 mi.R = it.R; mi.C = it.C; mi.row0 = it.row0; mi.col0 = it.col0; mi.wcols = it.wcols;
                 mi.nbands = it.nbands; mi.tr = it.tr;
                 mi.om_beta1 = h.om_beta1; mi.dq_beta1 = h.beta1 / QMAX_I8;
+                // the record written above comes before the arrival (same thread)
+                mbar_arrive_expect_tx(&sh->ready[buf], c_bytes + r_bytes);      // the one arrival `ready` waits for
+                bulk_g2s(sc, s.mfac_c + it.col0, c_bytes, &sh->ready[buf]);
+                bulk_g2s(sr, s.mfac + it.row0, r_bytes, &sh->ready[buf]);
             }
         };
         auto row_epilogue = [&](int item, int buf) {
@@ -103,10 +109,7 @@ __global__ void __launch_bounds__(M_ALL_THREADS, 1) k_moment_tile8_wide(StepArgs
                 rowpart[(int64_t)it.tc * it.R + it.row0 + i] = t;
             }
         };
-        auto publish = [&](int buf) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->ready[buf]);      // release: the writes above are visible to the waiters
-        };
+        auto publish = [&](int) {};      // `prepare` arrives on `ready` itself (with the factor slices' bytes)
         for (int j = 0; j < 2; ++j)
             if ((int)(blockIdx.x + j * gridDim.x) < n_items) { prepare(blockIdx.x + j * gridDim.x, j); publish(j); }
         int n = 0;
@@ -490,19 +493,17 @@ __global__ void __launch_bounds__(W_ALL_THREADS, 1) k_apply_flat8_wide(StepArgs 
         float* sr = s_rows + buf * 2 * W_TR;       // [0]: r / clip, [1]: R'
         float* sc = s_cols + buf * 2 * W_TC;       // [0]: c, [1]: C'
         if (!aborted) {
-            const bool clamp = d.flags & CAME_F_SQ_CLAMP, cr = d.flags & CAME_F_RESROW_CLAMP;
-            float mean = warp_vector_sum(s.rowblk, s.nbR, lane) / (float)R;
-            mean = guard_mean(mean, d.flags & CAME_F_SQ_FIX, clamp);
+            // r_i / clip and c_j come from the factor vectors k_s_finalize prepared for the momentum pass
+            const bool cr = d.flags & CAME_F_RESROW_CLAMP;
             float mean2 = warp_vector_sum(s.rowblk2, s.nbR, lane) / (float)R;
             mean2 = guard_mean(mean2, d.flags & CAME_F_RESROW_FIX, cr);
-            const float inv_clip = h.grad_scale / s.scal[1];      // the gradient scale enters u through the row factor
             for (int i = threadIdx.x; i < W_TR; i += W_CONSUMERS) {
                 const bool in = it.row0 + i < R;
-                sr[i] = in ? row_factor(s.vr[it.row0 + i], mean, clamp) * inv_clip : 0.0f;
+                sr[i] = in ? s.mfac[it.row0 + i] : 0.0f;
                 sr[W_TR + i] = in ? row_factor(s.Rr[it.row0 + i], mean2, cr) : 0.0f;
             }
             for (int i = threadIdx.x; i < it.wcols; i += W_CONSUMERS) {
-                sc[i] = col_factor(s.vc[it.col0 + i], clamp);
+                sc[i] = s.mfac_c[it.col0 + i];
                 sc[W_TC + i] = col_factor(s.Rc[it.col0 + i], d.flags & CAME_F_RESCOL_CLAMP);
             }
         }

@@ -49,12 +49,13 @@ struct MaItem {
     const unsigned char* a_src;
     const unsigned char* m_src;
     const unsigned char* x_src;
+    const unsigned char* b_src;      // flat-layout A item: the parameter rows (a_src holds the gradient rows)
     int64_t a_pitch, m_pitch, x_pitch;
     // M
     int8_t* m;
     float* m_absmax;
     float* colpart;
-    float om_beta1, dq_beta1;
+    float om_beta1, dq_beta1, beta1;
     int keep;             // the codes this item writes are marked evict-last in L2
     // A
     void* p;
@@ -185,7 +186,8 @@ __device__ __forceinline__ void ma_finalize_block(const StepArgs& a, int tensor,
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int idx = base + 32 * e;
-            if (idx < nvec) s.mfac_c[idx] = col_factor(v[e], d.flags & CAME_F_RESCOL_CLAMP);      // C'_j
+            // C'_j for the tensor's A items (the flat layout still needs c_j there: a vector of its own)
+            if (idx < nvec) (s.mfac_c2 ? s.mfac_c2 : s.mfac_c)[idx] = col_factor(v[e], d.flags & CAME_F_RESCOL_CLAMP);
         }
     }
 }
@@ -215,12 +217,18 @@ __device__ __forceinline__ void ma_drain(MaShared* sh, int stages) {
             if (mbar_try_wait(&sh->full[i], 0) || mbar_try_wait(&sh->full[i], 1)) break;
 }
 
-template <typename T>
+// FLAT = false: tile layout (the momentum is re-quantised per 16 x 16 tile by the M items; the A items read the new
+// codes).  FLAT = true: flat layout, column count a multiple of 256 (absmax per 256-column row segment): the M items
+// only produce the residual sums; the A items recompute the momentum from g and the old codes so that its un-quantised
+// value feeds the update, re-quantise it and update p (k_apply_flat8_wide's item: bands of 8 rows of g, p and codes).
+template <typename T, bool FLAT>
 __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepArgs a, const Work* __restrict__ work, int n_items,
                                                                           int* __restrict__ mcount, int* __restrict__ fcount,
                                                                           int* __restrict__ next_item, const Work* __restrict__ fwork,
                                                                           int n_fitems, int* __restrict__ next_fitem, int keep_pct) {
     constexpr int STAGES = WideCfg<T>::STAGES, STAGE = WideCfg<T>::STAGE, ROW = WideCfg<T>::ROW;
+    constexpr int FLB = 8;                                  // rows of a band of a flat-layout A item
+    static_assert(FLB * (2 * ROW + W_MROW) <= STAGE, "a flat A band fits a ring slot");
     extern __shared__ __align__(128) unsigned char smem[];
     MaShared* sh = reinterpret_cast<MaShared*>(smem + STAGES * STAGE);
     float* s_r = reinterpret_cast<float*>(sh + 1);      // [2][W_TR]   row factors of an item (M: r_i / clip, A: R'_i)
@@ -260,6 +268,29 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             const int nbands = it.nbands, nrows = it.R - it.row0;
             const uint32_t a_bytes = (uint32_t)it.wcols * sizeof(T), m_bytes = (uint32_t)it.wcols;
             const uint32_t x_bytes = x_src ? (uint32_t)(it.wcols >> 4) * sizeof(float) : 0u;
+            if (FLAT && it.kind == MA_KIND_A) {
+                // bands of 8 rows, three operands: lanes 0-7 the gradient rows, 8-15 the code rows, 16-23 the parameter rows
+                const unsigned char* b_src = it.b_src;
+                for (int band = 0; band < nbands; ++band, ++q) {
+                    if (q % MA_PRODUCERS != which) continue;
+                    const int slot = q % STAGES;
+                    if (q >= STAGES && !ma_wait(&sh->empty[slot], ((q / STAGES) - 1) & 1, sh, a, lane)) { ok = false; break; }
+                    const int rows = min(FLB, nrows - band * FLB);
+                    if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], (uint32_t)rows * (2 * a_bytes + m_bytes));
+                    __syncwarp();
+                    const int r = lane & 7, op = lane >> 3;
+                    if (r < rows && op < 3) {
+                        const int64_t row = band * FLB + r;
+                        unsigned char* st = smem + slot * STAGE;
+                        if (op == 0) bulk_g2s_hint(st + r * ROW, a_src + row * a_pitch, a_bytes, &sh->full[slot], stream_policy);
+                        else if (op == 1) bulk_g2s_hint(st + 2 * FLB * ROW + r * W_MROW, m_src + row * m_pitch, m_bytes, &sh->full[slot], stream_policy);
+                        else bulk_g2s_hint(st + FLB * ROW + r * ROW, b_src + row * a_pitch, a_bytes, &sh->full[slot], stream_policy);
+                    }
+                }
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive(&sh->done[buf]);
+                continue;
+            }
             for (int band = 0; band < nbands; ++band, ++q) {
                 if (q % MA_PRODUCERS != which) continue;
                 const int slot = q % STAGES;
@@ -347,13 +378,16 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
         // so do consecutive A items): filling an entry is a chain of dependent global loads, done once per tensor.
         struct TensorInfo {
             int tensor, R, C, ptiles_c, ntiles;
-            const unsigned char* a_base;      // g (M) or p (A)
+            const unsigned char* a_base;      // g (M, flat A) or p (tile A)
+            const unsigned char* b_base;      // p (flat A)
+            const float* fac_c2;              // flat A: C'_j (fac_c keeps c_j)
+            const float* fac_r0;              // flat A: mfac rows (r_i / clip)
             const unsigned char* m_base;
             const unsigned char* x_base;      // tile absmax
             float* colpart;
             const float* fac_r;               // M: mfac (r_i / clip); A: the fresh residual row vector Rr
             const float* fac_c;               // mfac_c
-            float om_beta1, dq_beta1, lr, wd_lr, decay_mul;
+            float om_beta1, dq_beta1, beta1, lr, wd_lr, decay_mul;
             int wd_mode;
             float mean;                       // A: guarded mean(Rr)
             bool clamp_row;
@@ -369,13 +403,15 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 const CameHyper& h = a.hyp[d.group];
                 t.tensor = w.tensor;
                 t.R = (int)d.rows; t.C = (int)d.cols; t.ptiles_c = s.ptiles_c; t.ntiles = s.ptiles_r * s.ptiles_c;
-                t.a_base = reinterpret_cast<const unsigned char*>(kind == MA_KIND_M ? d.g : d.p);
+                t.a_base = reinterpret_cast<const unsigned char*>((kind == MA_KIND_M || FLAT) ? d.g : d.p);
+                t.b_base = reinterpret_cast<const unsigned char*>(d.p);
+                t.fac_c2 = s.mfac_c2; t.fac_r0 = s.mfac;
                 t.m_base = reinterpret_cast<const unsigned char*>(d.m);
                 t.x_base = reinterpret_cast<const unsigned char*>(d.m_absmax);
                 t.colpart = s.colpart; t.fac_r = kind == MA_KIND_M ? s.mfac : s.Rr; t.fac_c = s.mfac_c;
                 t.mean = kind == MA_KIND_A ? s.scal[2] : 1.0f;
                 t.clamp_row = d.flags & CAME_F_RESROW_CLAMP;
-                t.om_beta1 = h.om_beta1; t.dq_beta1 = h.beta1 / QMAX_I8;
+                t.om_beta1 = h.om_beta1; t.dq_beta1 = h.beta1 / QMAX_I8; t.beta1 = h.beta1;
                 t.lr = h.lr; t.wd_lr = h.wd_lr; t.decay_mul = h.decay_mul;
                 t.wd_mode = h.weight_decay == 0.0f ? 0 : ((d.flags & CAME_F_WD_MUL2) ? 2 : ((d.flags & CAME_F_WD_ADD2) ? 3 : 1));
             }
@@ -385,13 +421,20 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             const int tr = tile / t.ptiles_c, tc = tile - tr * t.ptiles_c;
             const int row0 = tr * W_TR, col0 = tc * W_TC;
             const int wcols = min(W_TC, C - col0);
-            const int nbands = min(W_BANDS, (R - row0 + W_BAND - 1) / W_BAND);
+            const bool flat_a = FLAT && kind == MA_KIND_A;
+            const int nbands = flat_a ? min(W_TR / FLB, (R - row0 + FLB - 1) / FLB) : min(W_BANDS, (R - row0 + W_BAND - 1) / W_BAND);
             // The factor slices of the item come by bulk copies that complete on the record's `ready` barrier (the
             // waiters see them with the record): the column factors (c_j for M, C'_j for A) of the tile's columns and
             // the row factors (r_i / clip, R'_i) of its rows.  Rows past the end of the matrix receive whatever follows
             // in the scratch (the copy is rounded up to 16 bytes); the computing warps never use them.
             const uint32_t c_bytes = (uint32_t)wcols * sizeof(float);
-            const uint32_t r_bytes = kind == MA_KIND_M ? (uint32_t)((min(W_TR, R - row0) + 3) & ~3) * sizeof(float) : 0u;
+            const uint32_t r_bytes = (kind == MA_KIND_M || flat_a) ? (uint32_t)((min(W_TR, R - row0) + 3) & ~3) * sizeof(float) : 0u;
+            // a flat A item needs both pairs of factors: r_i / clip and c_j (bulk copies, as for an M item) in the record's
+            // first slices, R'_i (computed here) and C'_j (bulk copy) in the record's row-partial area, which an A item
+            // does not use otherwise
+            float* sr2 = s_row + buf * (W_WARPS * W_TR);
+            float* sc2 = sr2 + W_TR;
+            if (flat_a) sr = sr2;      // where the R'_i computed below go
             if (kind == MA_KIND_A) {
                 // R'_i = rsqrt(Rr_i / mean(Rr)) for the tile's rows (came_kernels.cu:313-332)
                 float rr[W_TR / 32];
@@ -409,20 +452,26 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 mi.a_pitch = (int64_t)C * sizeof(T); mi.m_pitch = C; mi.x_pitch = (int64_t)(C >> 4) * sizeof(float);
                 mi.a_src = t.a_base + (int64_t)row0 * mi.a_pitch + (int64_t)col0 * sizeof(T);
                 mi.m_src = t.m_base + (int64_t)row0 * mi.m_pitch + col0;
-                mi.x_src = kind == MA_KIND_A ? t.x_base + (int64_t)(row0 >> 4) * mi.x_pitch + (col0 >> 4) * sizeof(float) : nullptr;
+                mi.x_src = (kind == MA_KIND_A && !FLAT) ? t.x_base + (int64_t)(row0 >> 4) * mi.x_pitch + (col0 >> 4) * sizeof(float) : nullptr;
+                mi.b_src = t.b_base + (int64_t)row0 * mi.a_pitch + (int64_t)col0 * sizeof(T);
                 mi.m = reinterpret_cast<int8_t*>(const_cast<unsigned char*>(t.m_base));
                 mi.m_absmax = reinterpret_cast<float*>(const_cast<unsigned char*>(t.x_base));
                 mi.colpart = t.colpart;
-                mi.om_beta1 = t.om_beta1; mi.dq_beta1 = t.dq_beta1;
+                mi.om_beta1 = t.om_beta1; mi.dq_beta1 = t.dq_beta1; mi.beta1 = t.beta1;
                 mi.keep = (int64_t)tile * 100 >= (int64_t)t.ntiles * (100 - keep_pct);
-                mi.p = const_cast<unsigned char*>(t.a_base); mi.lr = t.lr; mi.wd_lr = t.wd_lr; mi.decay_mul = t.decay_mul;
+                mi.p = const_cast<unsigned char*>(flat_a ? t.b_base : t.a_base); mi.lr = t.lr; mi.wd_lr = t.wd_lr; mi.decay_mul = t.decay_mul;
                 mi.wd_mode = t.wd_mode;
                 // the record written above comes before the arrival (same thread); the factor vectors were written by
                 // ordinary stores of other CTAs: order them before the bulk copies
                 fence_async_global();
-                mbar_arrive_expect_tx(&sh->ready[buf], c_bytes + r_bytes);      // the one arrival `ready` waits for
+                mbar_arrive_expect_tx(&sh->ready[buf], c_bytes + r_bytes + (flat_a ? c_bytes : 0u));   // the one arrival `ready` waits for
                 bulk_g2s(sc, t.fac_c + col0, c_bytes, &sh->ready[buf]);
-                if (r_bytes) bulk_g2s(sr, t.fac_r + row0, r_bytes, &sh->ready[buf]);
+                if (flat_a) {
+                    bulk_g2s(s_r + buf * W_TR, t.fac_r0 + row0, r_bytes, &sh->ready[buf]);
+                    bulk_g2s(sc2, t.fac_c2 + col0, c_bytes, &sh->ready[buf]);
+                } else if (r_bytes) {
+                    bulk_g2s(sr, t.fac_r + row0, r_bytes, &sh->ready[buf]);
+                }
             }
         };
         auto epilogue = [&](int buf) {
@@ -565,7 +614,16 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
             int8_t* mdst = mi.m + (int64_t)(row0 + rsub) * C + col;
             float* amax_dst = mi.m_absmax + (int64_t)(row0 >> 4) * tile_cols + (col >> 4);
             const int64_t band_bytes = (int64_t)W_BAND * C;
-            float a_next = active ? amax_dst[0] : 0.0f;
+            float a_next = (active && !FLAT) ? amax_dst[0] : 0.0f;
+            // flat layout: one absmax per (row, 256-column segment); this lane's 4 rows of the band, one band ahead
+            const float* amax_flat = mi.m_absmax + (((int64_t)(row0 + rsub) * C + col) >> 8);
+            const int64_t flat_row_step = C >> 8;       // absmax entries per row
+            float af_next[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (FLAT && active) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (row0 + rsub + 4 * i < R) af_next[i] = amax_flat[(int64_t)(4 * i) * flat_row_step];
+            }
             const float* sr_k = sr + rsub;
             float* srow_k = srow + warp * W_TR + rsub;
 
@@ -580,8 +638,17 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 const unsigned char* sm = smem + slot * STAGE + W_BAND * ROW + cl;
                 const int brow = row0 + k * W_BAND;
                 const float a_old = a_next;
-                if (k + 1 < nbands) a_next = amax_dst[tile_cols];
+                if (!FLAT && k + 1 < nbands) a_next = amax_dst[tile_cols];
                 const u64 scb2 = splat(a_old * dq_beta1);      // a tile that was never written has absmax 0: scale 0
+                float af[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) af[i] = af_next[i];
+                if (FLAT && k + 1 < nbands) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (brow + W_BAND + rsub + 4 * i < R)
+                            af_next[i] = amax_flat[(int64_t)((k + 1) * W_BAND + 4 * i) * flat_row_step];
+                }
                 const bool full_band = brow + W_BAND <= R;
                 float rsum[4];
                 float A = 1.0f;
@@ -598,23 +665,27 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                         uint2 mv = *reinterpret_cast<const uint2*>(sm + r * W_MROW);
                         mv.x ^= 0x80808080u; mv.y ^= 0x80808080u;
                         const u64 ra2 = splat(live ? sr_k[4 * i] : 0.0f);
+                        const u64 sc_row2 = FLAT ? splat(af[i] * dq_beta1) : scb2;
                         u64 rs2 = F2ZERO;
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const u64 u2 = mul2(mul2(g2[j], ra2), cf2[j]);
-                            const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), scb2);
+                            const u64 mo2 = mul2(codes_to_f2(j < 2 ? mv.x : mv.y, (j & 1) * 2), sc_row2);
                             u64 mn = fma2(om2, u2, mo2);
                             u64 df2 = sub2(u2, mn);
                             if (!FULL && !live) { df2 = F2ZERO; mn = F2ZERO; }
                             colacc[j] = fma2(df2, df2, colacc[j]);
                             rs2 = fma2(df2, df2, rs2);
-                            amax = fmaxf(amax, fmaxf(fabsf(mn.x), fabsf(mn.y)));
-                            m2[i][j] = mn;
+                            if (!FLAT) {
+                                amax = fmaxf(amax, fmaxf(fabsf(mn.x), fabsf(mn.y)));
+                                m2[i][j] = mn;
+                            }
                         }
                         rsum[i] = rs2.x + rs2.y;
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->empty[slot]);      // the slot's bytes are in registers now
+                    if (FLAT) return;                  // nothing is written in the flat layout
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
                     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
@@ -646,7 +717,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                 };
                 if (full_band) band(std::true_type{});
                 else band(std::false_type{});
-                if (rsub == 0 && (c8 & 1) == 0) *amax_dst = A;     // one lane per tile
+                if (!FLAT && rsub == 0 && (c8 & 1) == 0) *amax_dst = A;     // one lane per tile
                 {
                     const bool up4 = (c8 & 4) != 0, up2 = (c8 & 2) != 0;
                     const float a0 = (up4 ? rsum[2] : rsum[0]) + __shfl_xor_sync(0xffffffffu, up4 ? rsum[0] : rsum[2], 4);
@@ -668,7 +739,109 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                     if (rsub == 0) *reinterpret_cast<float2*>(mi.colpart + (int64_t)mi.tr * C + col + 2 * j) = make_float2(lo, hi);
                 }
             }
-        } else if (kind == MA_KIND_A) {
+        } else if (FLAT) {
+            // ---- flat-layout apply tile (reference: kCameFactoredExpAvgResPrepare + kCameFactoredParamUpdate,
+            //      came_kernels.cu:2246-2305, 2487-2511): bands of 8 rows; warp w owns the 256-column segment (w & 3) of
+            //      rows 2 * (w >> 2) and 2 * (w >> 2) + 1 of the band: a warp = one flat block at a time ----
+            const int chunk = warp & 3, rpair = warp >> 2;
+            const int fcl = chunk * 256 + lane * 8;
+            const bool factive = fcl < mi.wcols;
+            const int fcol = mi.col0 + fcl;
+            const float* sr2 = s_row + buf * (W_WARPS * W_TR);      // R'_i
+            const float* sc2 = sr2 + W_TR;                          // C'_j
+            u64 cf2[4], cr2[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                cf2[j] = factive ? pk(sc[fcl + 2 * j], sc[fcl + 2 * j + 1]) : F2ZERO;
+                cr2[j] = factive ? pk(sc2[fcl + 2 * j], sc2[fcl + 2 * j + 1]) : F2ZERO;
+            }
+            const int wd_mode = mi.wd_mode;
+            const u64 om2 = splat(mi.om_beta1), dmul2 = splat(mi.decay_mul), nwdlr2 = splat(-mi.wd_lr), nlr2 = splat(-mi.lr);
+            const float beta1 = mi.beta1;
+            const int64_t blocks_per_row = C >> 8;
+            float* amax_blk = mi.m_absmax + (int64_t)(row0 + 2 * rpair) * blocks_per_row + (fcol >> 8);
+            int8_t* const m_base = mi.m;
+            T* const p_base = reinterpret_cast<T*>(mi.p);
+            float an[2] = {1.0f, 1.0f};
+            if (factive) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+                    if (row0 + 2 * rpair + t < R) an[t] = amax_blk[(int64_t)t * blocks_per_row];
+            }
+#pragma unroll 1
+            for (int k = 0; k < nbands; ++k, ++q) {
+                const int slot = q % STAGES;
+                const long long t_f0 = MA_CLOCK();
+                if (!ma_wait(&sh->full[slot], (uint32_t)((q / STAGES) & 1), sh, a, lane)) { ma_drain(sh, STAGES); return; }
+                if (prof) MA_PROF_ADD(7, MA_CLOCK() - t_f0);      // 7: A bands, wait for data
+                if (!factive) { __syncwarp(); if (lane == 0) mbar_arrive(&sh->empty[slot]); continue; }
+                const unsigned char* st = smem + slot * STAGE;
+                const int brow = row0 + k * FLB + 2 * rpair;
+                float a_old[2] = {an[0], an[1]};
+                if (k + 1 < nbands) {
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+                        if (brow + FLB + t < R) an[t] = amax_blk[(int64_t)((k + 1) * FLB + t) * blocks_per_row];
+                }
+                u64 g2[2][4], p2[2][4];
+                uint2 mv[2];
+                float ra[2], rr[2];
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const int r = 2 * rpair + t;
+                    wide_run8(reinterpret_cast<const T*>(st + r * ROW) + fcl, g2[t]);
+                    wide_run8(reinterpret_cast<const T*>(st + FLB * ROW + r * ROW) + fcl, p2[t]);
+                    mv[t] = *reinterpret_cast<const uint2*>(st + 2 * FLB * ROW + r * W_MROW + fcl);
+                    ra[t] = sr[k * FLB + r];
+                    rr[t] = sr2[k * FLB + r];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->empty[slot]);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (brow + t >= R) continue;       // uniform over the warp
+                    const uint32_t mx = mv[t].x ^ 0x80808080u, my = mv[t].y ^ 0x80808080u;
+                    const u64 ra2 = splat(ra[t]), scb2 = splat((a_old[t] / QMAX_I8) * beta1), rr2 = splat(rr[t]);
+                    u64 mn[4];
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const u64 u2 = mul2(mul2(g2[t][j], ra2), cf2[j]);
+                        mn[j] = fma2(om2, u2, mul2(codes_to_f2(j < 2 ? mx : my, (j & 1) * 2), scb2));
+                        amax = fmaxf(amax, fmaxf(fabsf(mn[j].x), fabsf(mn[j].y)));
+                    }
+                    amax = warp_max(amax);
+                    const float A = fix_absmax(amax);
+                    const int64_t off = (int64_t)(brow + t) * C + fcol;
+                    uint32_t out[2];
+                    if (recip_safe(A)) {      // uniform: A is a warp-wide value
+                        const u64 s127 = splat(QMAX_I8 / A);
+                        u64 y[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) y[j] = fma2(mn[j], s127, magic);
+                        out[0] = pack_codes4(y[0], y[1]);
+                        out[1] = pack_codes4(y[2], y[3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+                            out[e] = ((uint32_t)quant_i8_div(mn[2 * e].x, A) & 0xffu) | (((uint32_t)quant_i8_div(mn[2 * e].y, A) & 0xffu) << 8) |
+                                     (((uint32_t)quant_i8_div(mn[2 * e + 1].x, A) & 0xffu) << 16) | (((uint32_t)quant_i8_div(mn[2 * e + 1].y, A) & 0xffu) << 24);
+                    }
+                    *reinterpret_cast<uint2*>(m_base + off) = make_uint2(out[0], out[1]);
+                    if (lane == 0) amax_blk[(int64_t)(k * FLB + t) * blocks_per_row] = A;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const u64 upd = mul2(mul2(mn[j], rr2), cr2[j]);
+                        u64 pv = p2[t][j];
+                        if (wd_mode == 1) pv = fma2(nwdlr2, pv, pv);
+                        else if (wd_mode == 2) pv = round_pair<T>(mul2(pv, dmul2));
+                        else if (wd_mode == 3) pv = round_pair<T>(fma2(nwdlr2, pv, pv));
+                        p2[t][j] = fma2(nlr2, upd, pv);
+                    }
+                    wide_store8(p_base + off, p2[t]);
+                }
+            }
+        } else {
             // ---- apply tile (reference: kParamUpdateTiled came_kernels.cu:3332-3366, decay of :2678-2682) ----
             u64 cf2[4];
 #pragma unroll
@@ -748,21 +921,21 @@ template <typename T> static constexpr size_t ma_smem() {
            2 * (W_TR + W_TC + W_WARPS * W_TR) * sizeof(float) + 2 * sizeof(MaItem);
 }
 
-template <typename T>
+template <typename T, bool FLAT>
 static cudaError_t launch_ma(const StepArgs& a, const Work* work, int n, const Work* fwork, int nf, int* mcount, int* fcount,
                              int* next_item, cudaStream_t st) {
     // CAME_B200_MA_KEEP_PCT: share of a tensor's momentum tiles (the last written) whose codes are marked evict-last
     static const int keep_pct = [] { const char* e = getenv("CAME_B200_MA_KEEP_PCT"); return e ? atoi(e) : 25; }();
     const int sms = persistent_grid_limit();
     const size_t smem = ma_smem<T>();
-    cudaError_t e = cudaFuncSetAttribute(k_moment_apply_tile8<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k_moment_apply_tile8<T, FLAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     StepArgs args = a;
     int* next_fitem = next_item + 1;
     int keep = keep_pct;
     void* params[] = {&args, &work, &n, &mcount, &fcount, &next_item, &fwork, &nf, &next_fitem, &keep};
     // cooperative launch: every CTA of the grid is resident at once (CTAs wait for items other CTAs finish)
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_moment_apply_tile8<T>), dim3(n < sms ? n : sms),
+    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_moment_apply_tile8<T, FLAT>), dim3(n < sms ? n : sms),
                                        dim3(MA_ALL_THREADS), params, smem, st);
 }
 
@@ -770,9 +943,12 @@ cudaError_t launch_fused_ma(const KernelKey& key, const StepArgs& a, const Work*
                             int* mcount, int* fcount, int* next_item, cudaStream_t st) {
     if (n <= 0) return cudaSuccess;
     switch (key.g_dtype) {
-        case CAME_DT_F32: return launch_ma<float>(a, work, n, fwork, nf, mcount, fcount, next_item, st);
-        case CAME_DT_F16: return launch_ma<__half>(a, work, n, fwork, nf, mcount, fcount, next_item, st);
-        default: return launch_ma<__nv_bfloat16>(a, work, n, fwork, nf, mcount, fcount, next_item, st);
+        case CAME_DT_F32: return key.mode == CAME_MODE_FLAT8 ? launch_ma<float, true>(a, work, n, fwork, nf, mcount, fcount, next_item, st)
+                                                  : launch_ma<float, false>(a, work, n, fwork, nf, mcount, fcount, next_item, st);
+        case CAME_DT_F16: return key.mode == CAME_MODE_FLAT8 ? launch_ma<__half, true>(a, work, n, fwork, nf, mcount, fcount, next_item, st)
+                                                  : launch_ma<__half, false>(a, work, n, fwork, nf, mcount, fcount, next_item, st);
+        default: return key.mode == CAME_MODE_FLAT8 ? launch_ma<__nv_bfloat16, true>(a, work, n, fwork, nf, mcount, fcount, next_item, st)
+                                                  : launch_ma<__nv_bfloat16, false>(a, work, n, fwork, nf, mcount, fcount, next_item, st);
     }
 }
 

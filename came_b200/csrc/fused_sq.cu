@@ -157,6 +157,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
                     : reinterpret_cast<const float*>(d.sq_row)[row];
             }
             if (lane == 0) {
+                if (w.tile == 0) s.scal[3] = 0.0f;      // "a clamp binds": set by the finalize of this step, if at all
                 FaStrip& t = s_strip[sb];
                 t.vr = s.vr;
                 t.colpart = s.colpart + (int64_t)w.tile * RS * C;

@@ -139,8 +139,9 @@ struct WideShared {
     uint64_t ready[2];      // momentum pass: the helper warp has prepared the item of this buffer
     uint64_t done[2];       // momentum pass: every computing warp has finished the item of this buffer
     int abort;
-    int pad;
+    int pad[3];             // 112 bytes: what follows in shared memory stays 16-byte aligned (bulk-copy destinations)
 };
+static_assert(sizeof(WideShared) % 16 == 0, "the factor slices behind it are bulk-copy destinations");
 
 // Bounded wait that also gives up when another warp raised `abort`.  On its own timeout it records the failure
 // in the plan's status word and raises `abort`, so that every other waiter of the CTA leaves too.

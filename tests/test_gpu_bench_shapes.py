@@ -68,3 +68,31 @@ def test_full_size_matrix(shape, steps):
                            per_tensor_scale=True)
     _check_8bit(out, torch.bfloat16)
     _status_ok(opt)
+
+
+def test_camecuda_zero_rows_and_columns_take_the_clamped_path():
+    """CAMECUDA clamps its factors at 1e-30 (came_kernels.cu:577, 591-592).  The staged first pass derives the clip sum
+    from a closed form that holds while no clamp binds; rows and columns whose gradient is identically zero make one
+    bind (v = (1 - beta2) * eps0 ~ 1e-33), and the step must then fall back to the explicit sum and still match."""
+    import came_b200
+    from tests.parity_util import make_inputs, hyper_of, relerr
+    shapes = [(256, 1024), (130, 4096)]
+    params0, grads = make_inputs(shapes, torch.float32, 3, seed=71)
+    for gs in grads:
+        for g in gs:
+            g[10:20, :] = 0.0
+            g[:, 64:96] = 0.0
+    gp = [torch.nn.Parameter(p.cuda()) for p in params0]
+    opt = came_b200.CAMECUDA(gp, **H_DEFAULT)
+    cp = [p.clone() for p in params0]
+    sts = [orc.init_state(p, orc.CUDAFP) for p in cp]
+    for gs in grads:
+        for i, (p, g) in enumerate(zip(gp, gs)):
+            p.grad = g.cuda()
+            cp[i] = orc.step(cp[i], g, sts[i], hyper_of(H_DEFAULT), orc.CUDAFP)
+        opt.step()
+    _status_ok(opt)
+    for p, c, st in zip(gp, cp, sts):
+        assert relerr(p.data.cpu(), c) <= 1e-5
+        for k in ("exp_avg", "exp_avg_sq_row", "exp_avg_sq_col", "exp_avg_res_row", "exp_avg_res_col"):
+            assert relerr(opt.state[p][k].cpu(), st[k]) <= 1e-4, k

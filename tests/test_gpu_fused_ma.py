@@ -14,13 +14,13 @@ SHAPES = [(4096, 1024), (130, 11008), (257, 5632), (1024, 4096), (4096,), (2048,
           (16, 1024), (1000, 1088), (3000, 1024)]
 
 
-def _run(fused: bool, dtype, steps=3, wd=1e-2):
+def _run(fused: bool, dtype, steps=3, wd=1e-2, cls_name="CAME8bit"):
     import came_b200
     os.environ["CAME_B200_FUSED_MA"] = "1" if fused else "0"      # read when the plan is created
     try:
         gen = torch.Generator(device="cuda").manual_seed(3)
         params = [torch.nn.Parameter((torch.randn(s, device="cuda", generator=gen) * 0.02).to(dtype)) for s in SHAPES]
-        opt = came_b200.CAME8bit(params, **dict(H, weight_decay=wd))
+        opt = getattr(came_b200, cls_name)(params, **dict(H, weight_decay=wd))
         for k in range(steps):
             for i, p in enumerate(params):
                 p.grad = (torch.randn(p.shape, device="cuda", generator=gen) * 10.0 ** (-2 - (i % 4))).to(dtype)
@@ -35,11 +35,12 @@ def _run(fused: bool, dtype, steps=3, wd=1e-2):
         os.environ.pop("CAME_B200_FUSED_MA", None)
 
 
+@pytest.mark.parametrize("cls_name", ["CAME8bit", "CAME8bitFull"])      # tile layout, flat layout
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("wd", [1e-2, 0.0])
-def test_fused_equals_separate_passes(dtype, wd):
-    a, la = _run(True, dtype, wd=wd)
-    b, lb = _run(False, dtype, wd=wd)
+def test_fused_equals_separate_passes(cls_name, dtype, wd):
+    a, la = _run(True, dtype, wd=wd, cls_name=cls_name)
+    b, lb = _run(False, dtype, wd=wd, cls_name=cls_name)
     assert la < lb                      # one launch instead of three
     assert len(a) == len(b)
     for x, y in zip(a, b):
