@@ -16,7 +16,7 @@ CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 OBJDIR = os.path.join(CSRC, "build")
 LIB = os.path.join(PKG, "libcame_b200.so")
-SOURCES = ["capi.cu", "codec.cu", "factored.cu", "fast_tile8.cu", "fused_ma.cu", "fused_sq.cu", "nd.cu", "noalloc.cu", "nonfactored.cu"]
+SOURCES = ["capi.cu", "codec.cu", "factored.cu", "fast_tile8.cu", "fp_wide.cu", "fused_ma.cu", "fused_sq.cu", "nd.cu", "noalloc.cu", "nonfactored.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
 NVCC_FLAGS += os.environ.get("CAME_B200_NVCC_FLAGS", "").split()   # build-time experiment switches, e.g. -DCAME_TUNE

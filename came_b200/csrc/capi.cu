@@ -21,8 +21,9 @@ constexpr size_t ALIGN = 256;
 
 thread_local char g_err[512] = "";
 // CAME_B200_DISABLE_FAST=1 in the environment routes every tensor through the generic kernels (used by the
-// tests to compare the two implementations of a pass against each other)
-const bool g_disable_fast = [] { const char* e = getenv("CAME_B200_DISABLE_FAST"); return e && e[0] == '1'; }();
+// tests to compare the two implementations of a pass against each other).  Read whenever a plan is sized or created,
+// so that it must not change between came_b200_workspace_bytes and came_b200_plan_create of one plan.
+inline bool disable_fast() { const char* e = getenv("CAME_B200_DISABLE_FAST"); return e && e[0] == '1'; }
 
 // CAME_B200_WAVE_MB=n: run the momentum / apply passes in waves of tensors holding at most n MB of momentum state
 const size_t g_wave_bytes = [] { const char* e = getenv("CAME_B200_WAVE_MB"); return e ? (size_t)atol(e) << 20 : (size_t)0; }();
@@ -62,7 +63,7 @@ inline bool is_nd(const CameTensorDesc& d) { return d.cols != 0 && d.batch > 1; 
 // vector-path eligibility of a tensor for each kernel family
 struct VecFlags {
     int k;      // gradient reductions: 1 = runs of 8
-    int p2;     // momentum pass: 1 = runs of 16 over g and m, 2 = staged fast path (tile layout, cols % 256 == 0)
+    int p2;     // momentum pass: 1 = runs of 16 over g and m, 2 = staged fast path (tile / fp32 layout: cols % 64 == 0)
     int p3;     // apply pass: same over m and p
     int flat;   // flat apply: 1 = runs of 8 over g, m, p
     bool operator==(const VecFlags& o) const { return k == o.k && p2 == o.p2 && p3 == o.p3 && flat == o.flat; }
@@ -74,13 +75,14 @@ VecFlags vec_flags(const CameTensorDesc& d) {
     const bool c8 = d.cols % 8 == 0, c16 = d.cols % 16 == 0;
     // staged fast path of the momentum / apply passes: both or neither, as they share the tile geometry
     const bool all_aligned = aligned16(d.g) && aligned16(d.m) && aligned16(d.p);
-    const bool fast = !g_disable_fast && all_aligned &&
+    const bool fast = !disable_fast() && all_aligned &&
                       ((d.mode == CAME_MODE_TILE8 && d.cols % 64 == 0) ||
+                       (d.mode == CAME_MODE_FP32 && d.cols % 64 == 0) ||
                        (d.mode == CAME_MODE_FLAT8 && d.cols % 256 == 0 && d.g_dtype == d.p_dtype));
     v.k = c8 && aligned16(d.g);
     // (tensors with the 1e-30 clamps take the fused first pass too: its closed form for the clip sum holds whenever no
     // clamp binds, which the finalize checks; if one does, the two-pass sum runs for that tensor)
-    if (v.k && !g_disable_fast && fused_sq_eligible(d.cols, elem_bytes(d.g_dtype))) v.k = 2;
+    if (v.k && !disable_fast() && fused_sq_eligible(d.cols, elem_bytes(d.g_dtype))) v.k = 2;
     v.p2 = (c16 && aligned16(d.g) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.p3 = (c16 && aligned16(d.p) && aligned16(d.m)) ? (fast ? 2 : 1) : 0;
     v.flat = c8 && aligned16(d.g) && aligned16(d.p) && (reinterpret_cast<uintptr_t>(d.m) & 7u) == 0;
@@ -454,7 +456,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
     // Tensors of the tile layout on the staged path (same element type for g and p) take the fused kernel: their M, F
     // and A items form one list, a tensor's F and A items delayed by `lag` momentum items of later tensors.
     std::vector<char> fused(n_tensors, 0);
-    if (!g_disable_fast && fused_ma_enabled()) {
+    if (!disable_fast() && fused_ma_enabled()) {
         for (int i = 0; i < n_tensors; ++i)
             fused[i] = is2d(i) && D[i].g_dtype == D[i].p_dtype &&
                        ((D[i].mode == CAME_MODE_TILE8 && vf[i].p2 == 2 && vf[i].p3 == 2) ||

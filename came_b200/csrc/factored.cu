@@ -114,7 +114,7 @@ __device__ __forceinline__ float column_partial_sum(const float* __restrict__ pa
     float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     const bool vec = (n & 3) == 0 && (reinterpret_cast<uintptr_t>(part) & 15) == 0 && c0 + 8 <= n;
     if (vec) {
-#pragma unroll 4
+#pragma unroll 8
         for (int t = warp; t < parts; t += THREADS / 32) {
             const float4* p = reinterpret_cast<const float4*>(part + (int64_t)t * n + c0);
             const float4 x = p[0], y = p[1];
@@ -666,10 +666,12 @@ cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a,
         case KID_SUMSQ: return go(pick_sumsq(key.g_dtype, (key.variant >= 1)), a, work, n, st);
         case KID_S_FINALIZE: return go(k_s_finalize, a, work, n, st);
         case KID_MOMENT:
+            if (key.variant == 2 && key.mode == CAME_MODE_FP32) return launch_fp32_wide(kernel, key, a, work, n, st);
             if (key.variant == 2) return launch_fast_tile8(kernel, key, a, work, n, st);
             return go(pick_moment(key.g_dtype, key.mode, (key.variant >= 1)), a, work, n, st);
         case KID_RES_FINALIZE: return go(k_vec_finalize<true>, a, work, n, st);
         case KID_APPLY:
+            if (key.variant == 2 && key.mode == CAME_MODE_FP32) return launch_fp32_wide(kernel, key, a, work, n, st);
             if (key.variant == 2) return launch_fast_tile8(kernel, key, a, work, n, st);
             return go(pick_apply(key.p_dtype, key.mode, (key.variant >= 1)), a, work, n, st);
         case KID_FACTORS: return go(k_factors, a, work, n, st);

@@ -53,6 +53,9 @@ enum { MA_KIND_M = 0, MA_KIND_F = 1, MA_KIND_A = 2, MA_KIND_END = 3 };
 
 cudaError_t launch_factored(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                             cudaStream_t st);
+// fp32-state layout, staged momentum / apply passes (fp_wide.cu)
+cudaError_t launch_fp32_wide(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
+                             cudaStream_t st);
 cudaError_t launch_fast_tile8(int kernel, const KernelKey& key, const StepArgs& a, const Work* work, int n,
                               cudaStream_t st);
 // work: the M and A items in taking order; fwork: the F items in tensor order; next_item: two cursors (zeroed)
