@@ -84,6 +84,12 @@ def profile_shapes():
     return [(4096, 11008)] * 2 + [(11008, 4096)] * 2 + [(4096, 4096)] * 4 + [(4096,)] * 2
 
 
+def profile_fp32_shapes():
+    """A small case of the fp32-state kernels for profiler captures: a few matrices of the GPT-2-medium shapes
+    (54 M elements, 0.9 GB on the device; the fp32 gradients alone are 1.7x the L2)."""
+    return [(1024, 4096)] * 4 + [(4096, 1024)] * 4 + [(1024, 3072)] * 4 + [(8192, 1024)] + [(1024,)] * 2
+
+
 def cpu_sample_shapes():
     """The bounded sample of the Llama-7B workload that the CPU legs step: one tensor of each distinct shape with the
     number of times the shape occurs in the set (the full-set time is extrapolated as sum of time(shape) x count)."""
@@ -124,6 +130,8 @@ WORKLOADS = {
     "llama7b": (llama7b_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
     "llama7b_linear": (llama7b_linear_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
     "profile": (profile_shapes, "CAME8bit", "bfloat16", (0.9, 0.95, 0.995)),
+    "profile_camecuda": (profile_fp32_shapes, "CAMECUDA", "float32", (0.9, 0.999, 0.9999)),
+    "profile_memory": (profile_shapes, "CAME8bitMemory", "bfloat16", (0.9, 0.999, 0.9999)),
     "gpt2m_camecuda": (gpt2_medium_shapes, "CAMECUDA", "float32", (0.9, 0.999, 0.9999)),
     "llama1b_memory": (llama1b_shapes, "CAME8bitMemory", "bfloat16", (0.9, 0.999, 0.9999)),
     "llama1b_2d": (lambda: [s for s in llama1b_shapes() if len(s) == 2], "CAME8bit2D", "bfloat16", (0.9, 0.999, 0.9999)),
@@ -529,7 +537,7 @@ def run_gpu(args):
             "value": total_elems / (ms_step * 1e-3) / 1e9, "unit": "Gelem/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded; same gradient "
-            "tensors every step; 54 GB touched per step, far above the 126 MB L2)",
+            f"tensors every step; {step_bytes / 1e9:.1f} GB of operands per step on rank 0, far above the 126 MB L2)",
             "config": {"workload": args.workload, "optimizer": cls_name, "param_dtype": dtype_name,
                        "tensors": len(shapes), "elements": total_elems,
                        "parallelism": f"ownership x{world}, {n_buckets} buckets, gather of bucket b ({stepper.gather_mode}) overlapped "
