@@ -48,7 +48,6 @@ __device__ __forceinline__ void smem_run8(const float* p, u64* out) {
 constexpr int FA_MAX_SLOTS = 8;
 constexpr int FA_RING_BYTES = 192 * 1024;         // ring = slots x slot bytes; a batch (rb rows) fits one slot
 constexpr int FA_ALL_THREADS = FA_THREADS + 64;   // 16 computing warps, the copy-issuing warp, the row-finalize warp
-constexpr int FA_SYNC = FA_THREADS + 32;          // the computing warps and the row-finalize warp
 
 // What the computing warps and the row-finalize warp need to know about a strip, written to shared memory by
 // the copy-issuing warp before it starts the strip's copies (reading it from the tables in global memory would
@@ -64,13 +63,14 @@ struct FaStrip {
 // Shared bookkeeping of one CTA.  Ring: full / empty per slot.  Strips alternate between two buffers (record +
 // old row state): `ready` = the copy-issuing warp has filled the buffer, `done` = every computing warp and the
 // row-finalize warp are through with it.  `wready` = the row weights 1 / v_row of a batch are in shared memory
-// (two buffers, alternating by batch).
+// (two buffers, alternating by batch); `rowdone` = the row partials of a batch are complete.
 struct FaShared {
     uint64_t full[FA_MAX_SLOTS];
     uint64_t empty[FA_MAX_SLOTS];
     uint64_t ready[2];
     uint64_t done[2];
     uint64_t wready[2];
+    uint64_t rowdone[2];     // every computing warp has left its row partial of a batch (two buffers, alternating by batch)
     int abort;
     int pad;
 };
@@ -83,15 +83,6 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, FaShared
     }
     if (lane == 0) { atomicExch(a.status, STATUS_MBAR_TIMEOUT); atomicExch(&sh->abort, 1); }
     return false;
-}
-
-// batches of work item i, from the tables (only a warp that lost its strip record needs this, to keep in step
-// with the hardware barrier)
-__device__ __forceinline__ int fa_batches_of(const StepArgs& a, const Work* work, int i) {
-    const Work w = work[i];
-    const int rb = a.scr[w.tensor].fa_rb;
-    const int nrows = min(K_TR, (int)a.descs[w.tensor].rows - w.tile * K_TR);
-    return (nrows + rb - 1) / rb;
 }
 
 // Persistent CTA, one per SM; work item = a strip of 128 whole rows of one matrix.  Warps 0..15 compute, warp 16
@@ -109,10 +100,10 @@ __device__ __forceinline__ int fa_batches_of(const StepArgs& a, const Work* work
 //                 g^2 and g^2 / v_row down the columns.  RS = 2 (matrices of at most 2048 columns): the
 //                 threads form two sets that take the even and the odd rows of a batch, which keeps every
 //                 thread busy; each set leaves its own column partials.
-// Software pipeline: the row sweep of batch i+1 is issued before the column sweep of batch i, with one hardware
-// barrier per batch (computing warps + warp 17).  A computing warp therefore holds two ring slots.
-// After a failed wait a warp keeps walking its batches without touching data, so that it still meets the others at
-// the hardware barrier once per batch (nobody is left waiting).
+// Software pipeline: the row sweep of batch i+1 is issued before the column sweep of batch i; a computing warp
+// therefore holds two ring slots.  The warps meet only through mbarriers (data landed, row partials complete, row
+// weights ready, strip done), all with bounded, abort-aware waits: a warp whose wait runs out records it and leaves,
+// the others follow at their next wait, and the copy-issuing warp stays until the copies in flight have landed.
 template <typename TG, int NG, int RS>
 __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, const Work* __restrict__ work, int n_items,
                                                                     int n_slots, int slot_bytes) {
@@ -130,6 +121,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
             mbar_init(&sh->ready[i], 1);
             mbar_init(&sh->done[i], FA_WARPS + 1);
             mbar_init(&sh->wready[i], 1);
+            mbar_init(&sh->rowdone[i], FA_WARPS);
         }
         sh->abort = 0;
         mbar_init_fence();
@@ -192,33 +184,27 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
     if (warp == FA_WARPS + 1) {
         // row-finalize warp
         int gb = 0, n = 0;      // batches / strips gone through (buffer and phase selectors)
-        bool ok = true;
         for (int i = blockIdx.x; i < n_items; i += gridDim.x, ++n) {
             const int sb = n & 1;
-            if (ok && !fa_wait(&sh->ready[sb], (n >> 1) & 1, sh, a, lane)) ok = false;
-            int nbatch;
-            if (ok) nbatch = s_strip[sb].nbatch; else nbatch = fa_batches_of(a, work, i);
+            if (!fa_wait(&sh->ready[sb], (n >> 1) & 1, sh, a, lane)) return;
             const FaStrip& t = s_strip[sb];
-            const int rb = ok ? t.rb : 1, ppr = FA_WARPS / rb;
+            const int nbatch = t.nbatch, rb = t.rb, ppr = FA_WARPS / rb;
             for (int b = 0; b < nbatch; ++b, ++gb) {
-                named_sync(1, FA_SYNC);          // the row partials of batch b are complete
-                if (ok) {
-                    const int rows = min(rb, t.nrows - b * rb);
-                    if (lane < rows) {
-                        const float* part = s_part + (gb & 1) * FA_WARPS + lane * ppr;
-                        float sum = 0.0f;
-                        for (int q = 0; q < ppr; ++q) sum += part[q];
-                        const float mean = (sum * t.gs2 + t.eps0C) / t.fC;
-                        const float v = s_old[sb * K_TR + b * rb + lane] * t.beta2 + t.om_beta2 * mean;
-                        t.vr[t.row0 + b * rb + lane] = v;
-                        s_w[(gb & 1) * FA_RB + lane] = v > 0.0f ? 1.0f / v : 0.0f;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->wready[gb & 1]);
+                if (!fa_wait(&sh->rowdone[gb & 1], (gb >> 1) & 1, sh, a, lane)) return;      // the row partials of batch b
+                const int rows = min(rb, t.nrows - b * rb);
+                if (lane < rows) {
+                    const float* part = s_part + (gb & 1) * FA_WARPS + lane * ppr;
+                    float sum = 0.0f;
+                    for (int q = 0; q < ppr; ++q) sum += part[q];
+                    const float mean = (sum * t.gs2 + t.eps0C) / t.fC;
+                    const float v = s_old[sb * K_TR + b * rb + lane] * t.beta2 + t.om_beta2 * mean;
+                    t.vr[t.row0 + b * rb + lane] = v;
+                    s_w[(gb & 1) * FA_RB + lane] = v > 0.0f ? 1.0f / v : 0.0f;
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->wready[gb & 1]);
             }
-            named_sync(1, FA_SYNC);              // the strip's last column sweep is over
-            if (ok && lane == 0) mbar_arrive(&sh->done[sb]);
+            if (lane == 0) mbar_arrive(&sh->done[sb]);      // through with the strip's record and old row state
         }
         return;
     }
@@ -228,16 +214,10 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
     const int rset = threadIdx.x / ST, tis = threadIdx.x - rset * ST;
     int slot = 0, gb = 0, n = 0;      // ring position (advanced without a division), batches and strips gone through
     uint32_t phase = 0;
-    bool ok = true;
 
     for (int i = blockIdx.x; i < n_items; i += gridDim.x, ++n) {
         const int sb = n & 1;
-        if (ok && !fa_wait(&sh->ready[sb], (n >> 1) & 1, sh, a, lane)) ok = false;
-        if (!ok) {      // keep in step with the hardware barrier: one per batch plus one
-            const int nb = fa_batches_of(a, work, i);
-            for (int b = 0; b <= nb; ++b) named_sync(1, FA_SYNC);
-            continue;
-        }
+        if (!fa_wait(&sh->ready[sb], (n >> 1) & 1, sh, a, lane)) return;      // the status word is set
         const FaStrip& t = s_strip[sb];
         const int C = t.C, rb = t.rb, nrows = t.nrows, nbatch = t.nbatch;
         const int row_bytes = C * (int)sizeof(TG);
@@ -261,7 +241,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
             for (int e = 0; e < 4; ++e) { colb[j][e] = F2ZERO; colT[j][e] = F2ZERO; }
         }
 
-        auto row_sweep = [&](int b, int sl, float* part) {
+        auto row_sweep = [&](int b, int sl, float* part, uint64_t* rowdone) {
             const int rows = min(rb, nrows - b * rb);
             float acc_t = 0.0f;
             if (my_row < rows) {
@@ -287,7 +267,7 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
             }
 #pragma unroll
             for (int m = 16; m > 0; m >>= 1) acc_t += __shfl_xor_sync(0xffffffffu, acc_t, m);
-            if (lane == 0) part[warp] = acc_t;
+            if (lane == 0) { part[warp] = acc_t; mbar_arrive(rowdone); }      // same thread: the partial comes first
         };
         auto col_sweep = [&](int b, int sl, const float* wv) {
             const int rows = min(rb, nrows - b * rb);
@@ -313,25 +293,27 @@ __global__ void __launch_bounds__(FA_ALL_THREADS, 1) k_sqstat_fused(StepArgs a, 
             if (lane == 0) mbar_arrive(&sh->empty[sl]);
         };
 
-        if (fa_wait(&sh->full[slot], phase, sh, a, lane)) row_sweep(0, slot, s_part + (gb & 1) * FA_WARPS);
-        else ok = false;
-        named_sync(1, FA_SYNC);
+        // No CTA-wide barrier in the batch loop: a warp waits for its data (`full`), for the row weights of the batch it
+        // is about to sweep by columns (`wready`), and for nothing else, so the warps drift apart by up to a batch and
+        // their row sweeps (shared-memory loads, shuffles) overlap other warps' column sweeps (arithmetic).  Buffer
+        // reuse is safe without one: the partial / weight buffers of batch b are written again for batch b + 2, and a
+        // warp gets there only after its column sweep of batch b, i.e. after `wready` of batch b, which the
+        // row-finalize warp raises after reading the partials; it writes the weights of batch b + 2 only after every
+        // warp's row sweep of b + 2 (`rowdone`), which each warp issues after its column sweep of batch b.
+        if (!fa_wait(&sh->full[slot], phase, sh, a, lane)) return;
+        row_sweep(0, slot, s_part + (gb & 1) * FA_WARPS, &sh->rowdone[gb & 1]);
         for (int b = 0; b < nbatch; ++b, ++gb) {
             int nslot = slot + 1;
             uint32_t nphase = phase;
             if (nslot == n_slots) { nslot = 0; nphase ^= 1u; }
-            if (ok && b + 1 < nbatch) {
-                if (fa_wait(&sh->full[nslot], nphase, sh, a, lane)) row_sweep(b + 1, nslot, s_part + ((gb + 1) & 1) * FA_WARPS);
-                else ok = false;
+            if (b + 1 < nbatch) {
+                if (!fa_wait(&sh->full[nslot], nphase, sh, a, lane)) return;
+                row_sweep(b + 1, nslot, s_part + ((gb + 1) & 1) * FA_WARPS, &sh->rowdone[(gb + 1) & 1]);
             }
-            if (ok) {
-                if (fa_wait(&sh->wready[gb & 1], (gb >> 1) & 1, sh, a, lane)) col_sweep(b, slot, s_w + (gb & 1) * FA_RB);
-                else ok = false;
-            }
-            named_sync(1, FA_SYNC);
+            if (!fa_wait(&sh->wready[gb & 1], (gb >> 1) & 1, sh, a, lane)) return;
+            col_sweep(b, slot, s_w + (gb & 1) * FA_RB);
             slot = nslot; phase = nphase;
         }
-        if (!ok) continue;      // the status word is set; the partial sums of this strip stay unwritten
         // one set of column partials per (strip, row set)
 #pragma unroll
         for (int j = 0; j < NG; ++j) {
