@@ -392,7 +392,8 @@ def run_gpu(args):
     headline = cls_name == "CAME8bit"          # the per-kernel byte table below describes the tile-layout step
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
-    n_buckets = args.buckets if args.buckets > 0 else ({1: 1, 2: 8}.get(world, 4))
+    # push mode needs no pipelining of step and exchange: one bucket, one fused kernel over everything the rank owns
+    n_buckets = args.buckets if args.buckets > 0 else (1 if args.gather == "push" else {1: 1, 2: 8}.get(world, 4))
     # equal buckets (a half-size first and last bucket measured no better: 11.76 against 11.56 ms at N = 2)
     sp = ShardedParams(shapes, pdtype, dev, world, rank, buckets=n_buckets)
     gen = torch.Generator(device=dev).manual_seed(1234)
@@ -540,8 +541,10 @@ def run_gpu(args):
             f"tensors every step; {step_bytes / 1e9:.1f} GB of operands per step on rank 0, far above the 126 MB L2)",
             "config": {"workload": args.workload, "optimizer": cls_name, "param_dtype": dtype_name,
                        "tensors": len(shapes), "elements": total_elems,
-                       "parallelism": f"ownership x{world}, {n_buckets} buckets, gather of bucket b ({stepper.gather_mode}) overlapped "
-                                      f"with the step of bucket b+1" if world > 1 else "single GPU",
+                       "parallelism": (f"ownership x{world}, {n_buckets} bucket(s), the apply kernel stores the new weights into every peer's "
+                                       f"buffer (push)" if stepper.gather_mode == "push" else
+                                       f"ownership x{world}, {n_buckets} buckets, gather of bucket b ({stepper.gather_mode}) "
+                                       f"overlapped with the step of bucket b+1") if world > 1 else "single GPU",
                        "l2": "inputs larger than L2"},
             "roofline": roofline,
             "step_roofline": {"alg_bytes_per_step_rank0": step_bytes, "achieved": step_gbs, "peak": peak,
@@ -556,7 +559,8 @@ def run_gpu(args):
         }
         if world > 1:
             line["multi_gpu"] = {
-                "note": "value / ms_per_step time the overlapped step + all-gather; the two legs below are timed alone",
+                "note": "value / ms_per_step time the step with its weight exchange; the two legs below are timed alone "
+                        "(step without exchange; a full copy-engine exchange)",
                 "step_only_ms": ms_step_only, "step_only_gelem_s": total_elems / (ms_step_only * 1e-3) / 1e9,
                 "all_gather_ms": ag_ms, "all_gather_gbs_in": sp.gathered_bytes_per_rank() / (ag_ms * 1e-3) / 1e9,
                 "gather": stepper.gather_mode, "nvlink_peak_gbs": 770.0, "imbalance": imbalance(numels, sp.owners, world),
@@ -587,9 +591,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_ext"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buckets", type=int, default=0, help="exchange buckets at N > 1 (0: 8 at N = 2, 4 above, 1 at N = 1)")
-    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl"],
+    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "push", "nccl"],
                     help="exchange of updated weights at N > 1: copy-engine pulls over CUDA IPC mappings (auto: when every rank "
-                         "can map every peer, else NCCL), or NCCL all-gather")
+                         "can map every peer, else NCCL), stores into the peers' buffers by the apply kernel itself (push), "
+                         "or NCCL all-gather")
     ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
                     help="llama7b: the benchmark workload (BASELINE config 3); profile: a small case of the same kernels "
                          "for ncu; the others are BASELINE configs 2, 4 and 5")

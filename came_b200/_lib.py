@@ -77,6 +77,8 @@ SYMBOLS = {
     "came_b200_ipc_export": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
     "came_b200_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "came_b200_ipc_close": (C.c_int, [C.c_void_p]),
+    "came_b200_plan_set_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_int]),
+    "came_b200_plan_pushed": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_int]),
     "came_b200_plan_last_launches": (C.c_int, [C.c_void_p]),
     "came_b200_plan_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "came_b200_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_void_p]),

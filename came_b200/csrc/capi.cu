@@ -280,6 +280,10 @@ struct came_plan {
     std::vector<LaunchItem> launches;
     int last_launches = 0;
     bool has_fused_ma = false;
+    std::vector<char> fused;       // per tensor: stepped by the fused momentum / apply kernel
+    int n_push = 0;                // push mode: peers that receive every parameter the fused kernel updates
+    long long push_delta[MAX_PUSH_PEERS] = {};
+    uintptr_t push_lo = 0, push_hi = 0;      // the local buffer the pushed parameters must lie in
     bool timing = false;
     struct Timed { int kernel; cudaEvent_t t0, t1; };
     std::vector<Timed> timed;
@@ -466,6 +470,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
         const int grid = persistent_grid_limit();
         const size_t lag_a = (size_t)std::max(0, env_int("CAME_B200_MA_LAG", 5 * grid));
         const bool reverse_a = env_int("CAME_B200_MA_REVERSE", 1) != 0;
+        const bool interleave = env_int("CAME_B200_MA_INTERLEAVE", 1) != 0;
         for (int dm = 0; dm < 6; ++dm) {
             const int dt = CAME_DT_F32 + dm % 3, md = dm < 3 ? CAME_MODE_TILE8 : CAME_MODE_FLAT8;
             LaunchItem it{};
@@ -482,17 +487,30 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
                 for (int64_t k = 0; k < c; ++k)
                     work.push_back(Work{b.tensor, (int32_t)(((uint32_t)MA_KIND_A << 28) | (uint32_t)(reverse_a ? c - 1 - k : k))});
             };
+            // A released burst is dealt out one apply item per momentum item instead of all at once (CAME_B200_MA_INTERLEAVE=0:
+            // all at once): DRAM-bound apply items and issue-bound momentum items then share the GPU at all times
+            std::vector<Work> trickle;
+            size_t tnext = 0;
+            auto release = [&](const Burst& b) {
+                if (!interleave) { burst(b); return; }
+                const size_t before = work.size();
+                burst(b);
+                trickle.insert(trickle.end(), work.begin() + before, work.end());
+                work.resize(before);
+            };
             for (int i = 0; i < n_tensors; ++i) {
                 if (!fused[i] || D[i].g_dtype != dt || D[i].mode != md) continue;
                 const int64_t c = (int64_t)geo[i].ptiles_r * geo[i].ptiles_c;
                 for (int64_t k = 0; k < c; ++k) {
                     work.push_back(Work{i, (int32_t)(((uint32_t)MA_KIND_M << 28) | (uint32_t)k)});
                     ++emitted;
-                    while (next < pend.size() && pend[next].release <= emitted) burst(pend[next++]);
+                    while (next < pend.size() && pend[next].release <= emitted) release(pend[next++]);
+                    if (tnext < trickle.size()) work.push_back(trickle[tnext++]);
                 }
                 pend.push_back(Burst{emitted + lag_a, i});
             }
-            while (next < pend.size()) burst(pend[next++]);
+            while (next < pend.size()) release(pend[next++]);
+            while (tnext < trickle.size()) work.push_back(trickle[tnext++]);
             it.n = (int)(work.size() - it.work_off);
             it.work2_off = work.size();
             for (int i = 0; i < n_tensors; ++i) {
@@ -503,6 +521,7 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
             if (it.n > 0) { plan->launches.push_back(it); plan->has_fused_ma = true; }
         }
     }
+    plan->fused = fused;
     // The momentum pass, the residual finalize and the apply pass run wave by wave: a wave is a run of consecutive
     // tensors whose momentum state together stays below `wave_bytes`, so that the codes the momentum pass writes are
     // still in L2 when the apply pass reads them back (0: one wave, every pass covers all tensors).
@@ -566,6 +585,46 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
 
 void came_b200_plan_destroy(came_plan_t* plan) { delete plan; }
 
+// push mode: the whole parameter must lie inside the local buffer the peers mirror
+static bool pushed_param_in_range(const came_plan& plan, const CameTensorDesc& d) {
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(d.p);
+    const uintptr_t bytes = (uintptr_t)d.rows * (uintptr_t)(d.cols ? d.cols : 1) * (uintptr_t)(d.batch > 1 ? d.batch : 1) *
+                            (uintptr_t)elem_bytes(d.p_dtype);
+    return lo >= plan.push_lo && lo + bytes <= plan.push_hi;
+}
+
+int came_b200_plan_set_push(came_plan_t* plan, const void* local_base, size_t local_bytes, void* const* peer_bases, int n_peers) {
+    if (!plan) return fail(CAME_E_INVALID, "plan_set_push: plan is null");
+    if (n_peers == 0) { plan->n_push = 0; return CAME_OK; }
+    if (n_peers < 0 || n_peers > MAX_PUSH_PEERS) return fail(CAME_E_INVALID, "plan_set_push: %d peers outside [0, %d]", n_peers, MAX_PUSH_PEERS);
+    if (!local_base || !peer_bases || local_bytes == 0) return fail(CAME_E_INVALID, "plan_set_push: null argument");
+    came_plan probe;
+    probe.push_lo = reinterpret_cast<uintptr_t>(local_base);
+    probe.push_hi = probe.push_lo + local_bytes;
+    if (probe.push_lo % 16 != 0) return fail(CAME_E_INVALID, "plan_set_push: the local buffer is not 16-byte aligned");
+    for (int i = 0; i < plan->n_tensors; ++i)
+        if (plan->fused[i] && !pushed_param_in_range(probe, plan->descs[i]))
+            return fail(CAME_E_INVALID, "plan_set_push: tensor %d does not lie inside the local buffer", i);
+    long long delta[MAX_PUSH_PEERS];
+    for (int k = 0; k < n_peers; ++k) {
+        const uintptr_t pb = reinterpret_cast<uintptr_t>(peer_bases[k]);
+        if (!pb || pb % 16 != 0) return fail(CAME_E_INVALID, "plan_set_push: peer buffer %d is null or not 16-byte aligned", k);
+        if (pb < probe.push_hi && pb + local_bytes > probe.push_lo) return fail(CAME_E_INVALID, "plan_set_push: peer buffer %d overlaps the local one", k);
+        delta[k] = (long long)(pb - probe.push_lo);      // modular: the kernel adds it to a local address
+    }
+    plan->push_lo = probe.push_lo; plan->push_hi = probe.push_hi;
+    for (int k = 0; k < n_peers; ++k) plan->push_delta[k] = delta[k];
+    plan->n_push = n_peers;
+    return CAME_OK;
+}
+
+int came_b200_plan_pushed(const came_plan_t* plan, int* flags, int n_tensors) {
+    if (!plan || !flags) return fail(CAME_E_INVALID, "plan_pushed: null argument");
+    if (n_tensors != plan->n_tensors) return fail(CAME_E_INVALID, "plan_pushed: %d tensors given, plan has %d", n_tensors, plan->n_tensors);
+    for (int i = 0; i < n_tensors; ++i) flags[i] = plan->fused[i] ? 1 : 0;
+    return CAME_OK;
+}
+
 int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* const* p, int n_tensors, came_stream_t stream) {
     if (!plan) return fail(CAME_E_INVALID, "set_pointers: plan is null");
     if (n_tensors != plan->n_tensors) return fail(CAME_E_INVALID, "set_pointers: %d tensors given, plan has %d", n_tensors, plan->n_tensors);
@@ -577,6 +636,8 @@ int came_b200_plan_set_pointers(came_plan_t* plan, const void* const* g, void* c
         if (!next[i].g || !next[i].p) return fail(CAME_E_INVALID, "set_pointers: tensor %d: null pointer", i);
         if (!(vec_flags(next[i]) == plan->vflags[i]))
             return fail(CAME_E_INVALID, "set_pointers: tensor %d changes 16-byte alignment class; create a new plan", i);
+        if (plan->n_push > 0 && plan->fused[i] && !pushed_param_in_range(*plan, next[i]))
+            return fail(CAME_E_INVALID, "set_pointers: tensor %d leaves the buffer the push mode was set up for", i);
     }
     plan->descs.swap(next);
     const cudaError_t e = cudaMemcpyAsync(plan->ws + plan->L.off_descs, plan->descs.data(),
@@ -616,7 +677,8 @@ int came_b200_step(came_plan_t* plan, const CameHyper* hypers, int n_groups, cam
     StepArgs a{reinterpret_cast<const CameTensorDesc*>(plan->ws + plan->L.off_descs),
                reinterpret_cast<const Scratch*>(plan->ws + plan->L.off_scr),
                reinterpret_cast<const CameHyper*>(plan->ws + plan->L.off_hyp),
-               reinterpret_cast<int*>(plan->ws + plan->L.off_status)};
+               reinterpret_cast<int*>(plan->ws + plan->L.off_status), plan->n_push, 0, {}};
+    for (int k = 0; k < plan->n_push; ++k) a.push_delta[k] = plan->push_delta[k];
     const Work* wbase = reinterpret_cast<const Work*>(plan->ws + plan->L.off_work);
     int* sync = reinterpret_cast<int*>(plan->ws + plan->L.off_sync);
     if (plan->has_fused_ma) {      // the per-tensor item counters start every step at zero

@@ -838,7 +838,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                         else if (wd_mode == 3) pv = round_pair<T>(fma2(nwdlr2, pv, pv));
                         p2[t][j] = fma2(nlr2, upd, pv);
                     }
-                    wide_store8(p_base + off, p2[t]);
+                    wide_store8_push(p_base + off, p2[t], a);
                 }
             }
         } else {
@@ -891,7 +891,7 @@ __global__ void __launch_bounds__(MA_ALL_THREADS, 1) k_moment_apply_tile8(StepAr
                             else if (WD == 1) pv = fma2(nwdlr2, pv, pv);
                             p2[i][j] = fma2(nlr2, upd, pv);
                         }
-                        if (FULL || brow + rsub + 4 * i < R) wide_store8(pdst + (int64_t)(4 * i) * C, p2[i]);
+                        if (FULL || brow + rsub + 4 * i < R) wide_store8_push(pdst + (int64_t)(4 * i) * C, p2[i], a);
                     }
                 };
                 auto band_wd = [&](auto wd_tag) {

@@ -14,7 +14,13 @@ struct StepArgs {
     const Scratch* scr;            // device, one per tensor
     const CameHyper* hyp;          // device, one per param_group
     int* status;                   // device, one word: 0, or the STATUS_* code of a kernel that gave up a wait
+    // Push mode of the weight exchange: the apply items of the fused kernel also store every updated parameter at the
+    // same offset of n_push peer buffers (byte distances from the local buffer to each mapped peer buffer).
+    int n_push;
+    int pad;
+    long long push_delta[7];
 };
+constexpr int MAX_PUSH_PEERS = 7;
 
 // which template instance a work list is launched with
 struct KernelKey {

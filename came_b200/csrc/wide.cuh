@@ -72,6 +72,14 @@ __device__ __forceinline__ void wide_store8(float* dst, const u64* v) {
     upk(v[2], a, b); upk(v[3], c, d);
     reinterpret_cast<float4*>(dst)[1] = make_float4(a, b, c, d);
 }
+// the same, also at the same offset of every peer buffer of the push mode (plain stores over NVLink; n_push is 0
+// unless the plan was given peers)
+template <typename T>
+__device__ __forceinline__ void wide_store8_push(T* dst, const u64* v, const StepArgs& a) {
+    wide_store8(dst, v);
+    for (int k = 0; k < a.n_push; ++k)
+        wide_store8(reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(dst) + a.push_delta[k]), v);
+}
 // the value a T-typed parameter holds after a store, for a packed pair
 template <typename T> __device__ __forceinline__ u64 round_pair(u64 v);
 template <> __device__ __forceinline__ u64 round_pair<float>(u64 v) { return v; }

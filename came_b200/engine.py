@@ -143,6 +143,18 @@ class DevicePlan:
             stream = torch.cuda.current_stream(self.device).cuda_stream
             _lib.check(self.lib.came_b200_step(self.handle, arr, len(hypers), stream))
 
+    def set_push(self, local_base: int, local_bytes: int, peer_bases: list) -> None:
+        """Push mode of the weight exchange: from the next step on, the kernels that apply the update also store the new
+        parameters at the same offset of every peer buffer (addresses as mapped into this process)."""
+        arr = (C.c_void_p * max(1, len(peer_bases)))(*peer_bases)
+        _lib.check(self.lib.came_b200_plan_set_push(self.handle, local_base, local_bytes, arr, len(peer_bases)))
+
+    def pushed(self) -> list:
+        """Per tensor of the plan: True when the push mode delivers it."""
+        flags = (C.c_int * self.n)()
+        _lib.check(self.lib.came_b200_plan_pushed(self.handle, flags, self.n))
+        return [bool(f) for f in flags]
+
     def set_hyper(self, hypers: list) -> None:
         """Rewrites the hyper-parameter records a captured step uploads at every replay (no stream work)."""
         arr = (CameHyper * len(hypers))(*hypers)
@@ -189,6 +201,13 @@ class StepEngine:
 
     def __init__(self):
         self.plans: dict = {}
+        self.push = None      # (local_base, local_bytes, [peer bases]) applied to every plan that is (re)built
+
+    def set_push(self, local_base: int, local_bytes: int, peer_bases: list) -> None:
+        """Switches the push mode of the weight exchange on for the plans of this engine, present and future."""
+        self.push = (int(local_base), int(local_bytes), [int(b) for b in peer_bases])
+        for plan in self.plans.values():
+            plan.set_push(*self.push)
 
     def invalidate(self) -> None:
         for plan in self.plans.values():
@@ -207,6 +226,8 @@ class StepEngine:
                 if plan is not None:
                     plan.close()
                 plan = DevicePlan(dev, es)
+                if self.push is not None:
+                    plan.set_push(*self.push)
                 self.plans[dev] = plan
             ready.append(plan)
         for dev in [d for d in self.plans if d not in by_dev]:

@@ -224,6 +224,22 @@ class PeerGather:
                     s.flat.data_ptr() + lo * esz, self.peer_ptr[r] + lo * esz, n * esz, -1,
                     self.sides[k % len(self.sides)].cuda_stream))
 
+    def pull_ranges(self, ranges_by_rank: dict) -> None:
+        """Like pull_bucket for explicit pieces: {peer rank: [(first element, elements), ...]} of the flat buffer."""
+        s = self.sharded
+        ready = dist.all_reduce(self.flag, group=self.group, async_op=True)   # every rank has enqueued its step
+        for side in self.sides:
+            with torch.cuda.stream(side):
+                ready.wait()
+        esz = s.flat.element_size()
+        with torch.cuda.device(s.flat.device):
+            for k in range(1, s.world_size):
+                r = (s.rank + k) % s.world_size
+                for lo, n in ranges_by_rank.get(r, ()):
+                    _lib.check(self._lib.came_b200_peer_copy_async(
+                        s.flat.data_ptr() + lo * esz, self.peer_ptr[r] + lo * esz, n * esz, -1,
+                        self.sides[k % len(self.sides)].cuda_stream))
+
     def finish(self) -> None:
         """Current stream: wait for this rank's pulls.  That the peers have finished pulling FROM this rank is only
         needed before this rank's weights are rewritten: the all-reduce that says so is started here and waited
@@ -244,12 +260,16 @@ class ShardedStepper:
     """One optimizer per bucket over the tensors this rank owns; `step()` steps bucket after bucket and starts the
     all-gather of a bucket's updated weights as soon as its step kernels are enqueued, so that the gather of
     bucket b travels over NVLink while bucket b+1 is being stepped.  `gather_mode`: "nccl" (in-place
-    all_gather_into_tensor per bucket) or "peer" (copy-engine pulls over CUDA IPC mappings, see PeerGather)."""
+    all_gather_into_tensor per bucket), "peer" (copy-engine pulls over CUDA IPC mappings, see PeerGather) or "push":
+    the kernel that applies a tensor's update stores the new weights into every peer's buffer as it goes (plain stores
+    over NVLink into the same IPC mappings), so there is no separate exchange pass for those tensors; what the fused
+    kernel does not step (1-D tensors, odd shapes) is still pulled, and one small all-reduce after the step orders
+    every rank's stores before anybody reads the weights."""
 
     def __init__(self, sharded: ShardedParams, params_by_index: dict, make_optimizer, gather_mode: str = "nccl",
                  group=None):
-        if gather_mode not in ("nccl", "peer", "auto"):
-            raise ValueError("gather_mode must be 'nccl', 'peer' or 'auto'")
+        if gather_mode not in ("nccl", "peer", "push", "auto"):
+            raise ValueError("gather_mode must be 'nccl', 'peer', 'push' or 'auto'")
         self.sharded, self.group = sharded, group
         self.opts = []
         for b in range(sharded.n_buckets):
@@ -264,16 +284,80 @@ class ShardedStepper:
             ok = torch.tensor([0.0 if self.peer.error else 1.0], device=sharded.flat.device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
             if ok.item() == 1.0:
-                self.gather_mode = "peer"
+                self.gather_mode = "push" if gather_mode == "push" else "peer"
             else:
                 err = self.peer.error
                 self.peer.close()
                 self.peer = None
-                if gather_mode == "peer":
+                if gather_mode in ("peer", "push"):
                     raise RuntimeError(f"peer mapping of the parameter buffers failed on some rank: {err}")
+        self._push_ranges = None      # push mode: {peer rank: [(first element, elements)]} still to be pulled
+        if self.gather_mode == "push" and sharded.world_size - 1 > 7:
+            raise ValueError("push mode serves at most 7 peers")
+
+    def _push_args(self):
+        s = self.sharded
+        peers = [self.peer.peer_ptr[r] for r in range(s.world_size) if r != s.rank]
+        return s.flat.data_ptr(), s.flat.numel() * s.flat.element_size(), peers
+
+    def _set_push(self, on: bool) -> None:
+        base, nbytes, peers = self._push_args()
+        for o in self.opts:
+            if o is not None:
+                o._engine.set_push(base, nbytes, peers if on else [])
+
+    def _setup_push(self) -> None:
+        """First step in push mode (the gradients exist by now): build the plans, learn which tensors the kernels
+        deliver themselves, tell the peers, and work out what is left to pull from each of them."""
+        s = self.sharded
+        mine = {}
+        for b, o in enumerate(self.opts):
+            idx = s.owned_in_bucket(b)
+            if o is None:
+                continue
+            o.prime_for_cuda_graph()
+            plans = list(o._engine.plans.values())
+            flags = plans[0].pushed() if len(plans) == 1 and plans[0].n == len(idx) else [False] * len(idx)
+            if not any(flags):
+                flags = [False] * len(idx)
+            mine.update(dict(zip(idx, flags)))
+        everyone = [None] * s.world_size
+        dist.all_gather_object(everyone, mine, group=self.group)
+        pushed = {}
+        for d in everyone:
+            pushed.update(d)
+        self._set_push(True)
+        ranges = {}
+        for i, (r, view) in enumerate(zip(s.owners, s.views)):
+            if r == s.rank or pushed.get(i, False):
+                continue
+            lo = (view.data_ptr() - s.flat.data_ptr()) // s.flat.element_size()
+            lst = ranges.setdefault(r, [])
+            if lst and lst[-1][0] + lst[-1][1] == lo:
+                lst[-1] = (lst[-1][0], lst[-1][1] + view.numel())
+            else:
+                lst.append((lo, view.numel()))
+        self._push_ranges = ranges
 
     def step(self, gather: bool = True):
         works = []
+        if self.gather_mode == "push":
+            if self._push_ranges is None:
+                self._setup_push()
+            self.peer.before_step()
+            if not gather:
+                self._set_push(False)
+            for opt in self.opts:
+                if opt is not None:
+                    opt.step()
+            if not gather:
+                self._set_push(True)
+                return
+            # one all-reduce after every rank's step kernels: the stores into this rank's buffer are complete when it
+            # is; the pieces no kernel delivers are pulled behind it
+            self.peer.pull_ranges(self._push_ranges)
+            self.peer.finish()
+            return
         if self.peer is not None:
             self.peer.before_step()
         for b, opt in enumerate(self.opts):

@@ -241,6 +241,22 @@ int came_b200_ipc_export(const void* ptr, unsigned char handle[CAME_B200_IPC_HAN
 int came_b200_ipc_open(const unsigned char handle[CAME_B200_IPC_HANDLE_BYTES], void** base);
 int came_b200_ipc_close(void* base);
 
+/*
+ * Push mode of the weight exchange (no counterpart in the reference): the step itself delivers the updated weights.
+ * `local_base` / `local_bytes` describe the buffer of the current device that holds the parameters of this plan, and
+ * `peer_bases[k]` (k < n_peers <= 7) the same buffer of peer k as mapped into this process (came_b200_ipc_open:
+ * base + offset).  From the next came_b200_step on, the kernel that applies the update of a tensor also stores every
+ * new value at the same offset of every peer buffer, with plain stores over NVLink, for the tensors that
+ * came_b200_plan_pushed reports (those the fused momentum / apply kernel steps); the others still have to be copied
+ * (came_b200_peer_copy_async).  The stores are complete when the step's kernels are: order a cross-process
+ * synchronisation after the step on `stream` before a peer reads them.  Every such tensor must lie inside the local
+ * buffer (checked here and by came_b200_plan_set_pointers); n_peers == 0 switches the mode off.
+ */
+int came_b200_plan_set_push(came_plan_t* plan, const void* local_base, size_t local_bytes, void* const* peer_bases,
+                            int n_peers);
+/* flags[i] = 1 when tensor i of the plan is delivered by the push mode once it is switched on, else 0 */
+int came_b200_plan_pushed(const came_plan_t* plan, int* flags, int n_tensors);
+
 /* error codes */
 #define CAME_OK 0
 #define CAME_E_INVALID (-1)   /* bad argument / descriptor; see came_b200_last_error() */

@@ -1,5 +1,6 @@
-"""Two ranks on two GPUs of one box: the copy-engine gather (CUDA IPC mappings, plain device-to-device copies)
-must leave exactly the bytes the NCCL all-gather leaves.  Skipped on a box with a single GPU."""
+"""Two ranks on two GPUs of one box: the copy-engine gather (CUDA IPC mappings, plain device-to-device copies) and the
+push mode (the apply kernel stores the new weights into the peers' buffers itself) must leave exactly the bytes the
+NCCL all-gather leaves.  Skipped on a box with a single GPU."""
 import os
 import socket
 
@@ -28,7 +29,7 @@ def _worker(rank, world, port, out):
         from came_b200.partition import ShardedParams, ShardedStepper
         dev = torch.device("cuda", rank)
         results = {}
-        for mode in ("nccl", "peer"):
+        for mode in ("nccl", "peer", "push"):
             sp = ShardedParams(SHAPES, torch.bfloat16, dev, world, rank, buckets=2)
             gen = torch.Generator(device=dev).manual_seed(3)
             for v in sp.views:
@@ -44,7 +45,7 @@ def _worker(rank, world, port, out):
             torch.cuda.synchronize()
             results[mode] = sp.flat.clone()
             dist.barrier()
-        same = torch.equal(results["nccl"], results["peer"])
+        same = torch.equal(results["nccl"], results["peer"]) and torch.equal(results["nccl"], results["push"])
         flag = torch.tensor([1.0 if same else 0.0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
