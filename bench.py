@@ -392,23 +392,42 @@ def run_gpu(args):
     headline = cls_name == "CAME8bit"          # the per-kernel byte table below describes the tile-layout step
     numels = [math.prod(s) for s in shapes]
     total_elems = sum(numels)
-    # push mode needs no pipelining of step and exchange: one bucket, one fused kernel over everything the rank owns
-    n_buckets = args.buckets if args.buckets > 0 else (1 if args.gather == "push" else {1: 1, 2: 8}.get(world, 4))
-    # equal buckets (a half-size first and last bucket measured no better: 11.76 against 11.56 ms at N = 2)
-    sp = ShardedParams(shapes, pdtype, dev, world, rank, buckets=n_buckets)
-    gen = torch.Generator(device=dev).manual_seed(1234)
-    # every rank initialises every weight identically (same seed), as after a broadcast at start-up
-    for v in sp.views:
-        v.copy_((torch.randn(v.shape, generator=gen, device=dev) * 0.02).to(pdtype))
-    params = [torch.nn.Parameter(sp.views[i]) for i in sp.owned]
-    ggen = torch.Generator(device=dev).manual_seed(99 + rank)
     scale_gen = torch.Generator().manual_seed(7)
     scales = [10.0 ** float(torch.empty(1).uniform_(-5, -2, generator=scale_gen)) for _ in shapes]
-    for p, i in zip(params, sp.owned):
-        p.grad = (torch.randn(p.shape, generator=ggen, device=dev) * scales[i]).to(pdtype)
-    by_index = dict(zip(sp.owned, params))
-    stepper = ShardedStepper(sp, by_index, lambda ps: getattr(came_b200, cls_name)(ps, **dict(HYPER, betas=betas)),
-                             gather_mode=args.gather)
+
+    def build(gather, n_buckets):
+        # equal buckets (a half-size first and last bucket measured no better: 11.76 against 11.56 ms at N = 2)
+        sp = ShardedParams(shapes, pdtype, dev, world, rank, buckets=n_buckets)
+        gen = torch.Generator(device=dev).manual_seed(1234)
+        # every rank initialises every weight identically (same seed), as after a broadcast at start-up
+        for v in sp.views:
+            v.copy_((torch.randn(v.shape, generator=gen, device=dev) * 0.02).to(pdtype))
+        params = [torch.nn.Parameter(sp.views[i]) for i in sp.owned]
+        ggen = torch.Generator(device=dev).manual_seed(99 + rank)
+        for p, i in zip(params, sp.owned):
+            p.grad = (torch.randn(p.shape, generator=ggen, device=dev) * scales[i]).to(pdtype)
+        by_index = dict(zip(sp.owned, params))
+        stepper = ShardedStepper(sp, by_index, lambda ps: getattr(came_b200, cls_name)(ps, **dict(HYPER, betas=betas)),
+                                 gather_mode=gather)
+        return sp, params, stepper
+
+    # Exchange mode and buckets.  "push" (the apply kernel stores into the peers' buffers) needs no pipelining of step and
+    # exchange: one bucket, one fused kernel over everything the rank owns; stores issued by SMs reach about 600 GB/s per
+    # GPU against 735 GB/s of the copy engines, so it wins only where one peer is served (N = 2: 11.3 against 12.0 ms).
+    # "auto" therefore asks for it at N = 2 and for the copy-engine pulls elsewhere (8 buckets at N = 2, 4 above).
+    gather = args.gather
+    if gather == "auto" and world == 2 and args.buckets <= 0:
+        gather = "push"
+    n_buckets = args.buckets if args.buckets > 0 else (1 if gather == "push" else {1: 1, 2: 8}.get(world, 4))
+    try:
+        sp, params, stepper = build(gather, n_buckets)
+    except RuntimeError:
+        if args.gather != "auto":
+            raise
+        # (every rank sees the same failure: the set-up's collectives make them agree)
+        torch.cuda.empty_cache()
+        n_buckets = {1: 1, 2: 8}.get(world, 4)
+        sp, params, stepper = build("auto", n_buckets)
     owned_elems = sum(numels[i] for i in sp.owned)
     owned_2d = sum(numels[i] for i in sp.owned if len(shapes[i]) == 2)
     owned_1d = owned_elems - owned_2d
