@@ -414,10 +414,10 @@ def run_gpu(args):
     # Exchange mode and buckets.  "push" (the apply kernel stores into the peers' buffers) needs no pipelining of step and
     # exchange: one bucket, one fused kernel over everything the rank owns.  Stores issued by SMs reach 600-640 GB/s per
     # GPU against 735 GB/s of the copy engines, but nothing is filled, drained or read twice from HBM: measured 11.3
-    # against 11.9 ms at N = 2 and 15.8 against 16.2 ms at N = 4.  "auto" asks for it at the world sizes it was measured
-    # at and for the copy-engine pulls elsewhere (8 buckets at N = 2, 4 above).
+    # against 11.9 ms at N = 2, 15.8 against 16.2 ms at N = 4, 18.3 against 18.5 ms at N = 8.  "auto" asks for it at the
+    # world sizes it was measured at and for the copy-engine pulls elsewhere (8 buckets at N = 2, 4 above).
     gather = args.gather
-    if gather == "auto" and world in (2, 4) and args.buckets <= 0:
+    if gather == "auto" and world in (2, 4, 8) and args.buckets <= 0:
         gather = "push"
     n_buckets = args.buckets if args.buckets > 0 else (1 if gather == "push" else {1: 1, 2: 8}.get(world, 4))
     try:
