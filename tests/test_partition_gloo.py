@@ -153,6 +153,10 @@ def _fallback_worker(rank, world, port, out_dir):
             assert float(v.flatten()[0]) == float(o + 1)
         with pytest.raises(RuntimeError):
             ShardedStepper(sp, {i: i for i in sp.owned}, Noop, gather_mode="peer")
+        with pytest.raises(RuntimeError):      # the push mode needs the same mappings
+            ShardedStepper(sp, {i: i for i in sp.owned}, Noop, gather_mode="push")
+        with pytest.raises(ValueError):
+            ShardedStepper(sp, {i: i for i in sp.owned}, Noop, gather_mode="bogus")
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
@@ -160,7 +164,7 @@ def _fallback_worker(rank, world, port, out_dir):
 
 def test_exchange_mode_falls_back_consistently_when_one_rank_cannot_export(tmp_path):
     """`auto`: a rank whose export fails still joins every collective of the set-up, and all ranks end in the NCCL
-    (here: gloo) mode; `peer` raises on every rank."""
+    (here: gloo) mode; `peer` and `push` raise on every rank."""
     world = 2
     mp.spawn(_fallback_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all(os.path.exists(os.path.join(str(tmp_path), f"ok{r}")) for r in range(world))
