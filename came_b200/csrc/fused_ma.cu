@@ -1,4 +1,5 @@
-// Momentum pass, residual finalize and apply pass of the tile layout as ONE persistent kernel.
+// Momentum pass, residual finalize and apply pass of the tile layout (and of the flat layout whose column count is a
+// multiple of 256) as ONE persistent kernel.
 //
 // Run as three launches over all tensors, each pass ends in a tail (a work item keeps an SM for 12 us) and the
 // issue-bound momentum pass and the DRAM-bound apply pass never share the GPU.  Here the work items of every tensor
@@ -10,7 +11,13 @@
 //      C'_j; the tensor's last block adds the mean of the row vector        (k_vec_finalize<true>'s item)
 //
 //   list 1:  M(t0) M(t1)[`lag` items] A(t0) M(t1)[rest] M(t2)[...] A(t1) ...      computing warps, through the ring
+//            (once a tensor's apply items are due they are dealt out one per momentum item, so that the DRAM-bound
+//            and the issue-bound items share the GPU at all times)
 //   list 2:  F(t0) F(t1) ...                                                        one finalizer warp per CTA
+//
+// Push mode (StepArgs::n_push > 0, several GPUs): an A item stores every new parameter into the local buffer and, at
+// the same offset, into the mapped buffers of the peers: the weight exchange of a data-parallel job becomes part of the
+// step.  Plain stores; no kernel here reads a peer's memory.
 //
 // A CTA takes the next item of a list whenever it has room for it (two cursors in global memory), so the load
 // balances itself.  An F item needs every M item of its tensor, an A item every F item: per-tensor counters in global
