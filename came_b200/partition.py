@@ -151,7 +151,8 @@ class PeerGather:
     Ordering between ranks comes from one-element all-reduces (NCCL, a few microseconds): a rank may read a peer's
     piece of bucket b only after the peer has finished stepping it, and nobody may start the next step (which
     rewrites its own pieces) before every peer has pulled them.  One process per GPU, all GPUs of one box visible
-    to every process."""
+    to every process.  The push mode of ShardedStepper uses the same mappings the other way round: the step's kernels
+    store into them, and only what they do not deliver is pulled (`pull_ranges`)."""
 
     def __init__(self, sharded: ShardedParams, group=None):
         import ctypes as C
