@@ -307,6 +307,12 @@ class ShardedStepper:
             if o is not None:
                 o._engine.set_push(base, nbytes, peers if on else [])
 
+    def reset_push(self) -> None:
+        """Push mode: forget which tensors the kernels deliver.  The next `step()` works it out again (a collective:
+        call this on every rank) -- needed when the tensors of an optimizer, their dtypes or their alignment changed
+        after the first step, since a tensor that leaves the fused kernel must be pulled from then on."""
+        self._push_ranges = None
+
     def _setup_push(self) -> None:
         """First step in push mode (the gradients exist by now): build the plans, learn which tensors the kernels
         deliver themselves, tell the peers, and work out what is left to pull from each of them."""
