@@ -430,15 +430,42 @@ class Zero1Step:
     `grad_flat` / `grad_views` come from `ShardedParams.like_flat()`: every rank writes its local gradients of ALL
     parameters there; the parameters of the optimizers must have their `.grad` set to the views of the tensors the rank
     owns.  Gradients are summed; give the optimizers' param_groups `grad_scale = 1 / world_size` for the mean (the
-    scale is applied as the kernels read the gradients).  The exchange inside a captured sequence is the NCCL
-    all-gather (collectives are captured as graph nodes)."""
+    scale is applied as the kernels read the gradients).  The exchange is that of the stepper: the NCCL all-gather per
+    bucket (collectives are captured as graph nodes), or, for a stepper in push mode, the stores of the step's own
+    kernels followed by one small all-reduce."""
 
     def __init__(self, stepper: "ShardedStepper", grad_flat: torch.Tensor, group=None):
         self.stepper, self.sharded, self.grad_flat, self.group = stepper, stepper.sharded, grad_flat, group
         self.graph = None
 
+    def _run_push(self) -> None:
+        """Push mode of the stepper: reduce-scatter of every bucket, the step (whose kernels store the new weights into
+        the peers' buffers), one all-reduce that orders every rank's stores, the pieces no kernel delivers pulled by
+        copies, one all-reduce that says everybody has pulled -- all on the current stream, so the sequence can be
+        captured as it is."""
+        s, st = self.sharded, self.stepper
+        if st._push_ranges is None:
+            st._setup_push()
+        for b in range(s.n_buckets):
+            s.reduce_scatter_bucket(self.grad_flat, b, group=self.group)
+        for opt in st.opts:
+            if opt is not None:
+                opt.step()
+        dist.all_reduce(st.peer.flag, group=self.group)
+        esz = s.flat.element_size()
+        stream = torch.cuda.current_stream(s.flat.device).cuda_stream
+        with torch.cuda.device(s.flat.device):
+            for r, ranges in st._push_ranges.items():
+                for lo, n in ranges:
+                    _lib.check(st.peer._lib.came_b200_peer_copy_async(
+                        s.flat.data_ptr() + lo * esz, st.peer.peer_ptr[r] + lo * esz, n * esz, -1, stream))
+        dist.all_reduce(st.peer.flag, group=self.group)
+
     def run(self) -> None:
         s = self.sharded
+        if self.stepper.gather_mode == "push":
+            self._run_push()
+            return
         for b, opt in enumerate(self.stepper.opts):
             s.reduce_scatter_bucket(self.grad_flat, b, group=self.group)
             if opt is not None:
@@ -453,6 +480,8 @@ class Zero1Step:
         for opt in self.stepper.opts:
             if opt is not None:
                 opt.prime_for_cuda_graph()
+        if self.stepper.gather_mode == "push" and self.stepper._push_ranges is None:
+            self.stepper._setup_push()      # host-side collectives: not inside the capture
         side = torch.cuda.Stream(device=self.sharded.flat.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

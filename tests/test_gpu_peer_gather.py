@@ -72,7 +72,7 @@ def test_peer_gather_equals_nccl_all_gather():
     assert out.get(timeout=10) is True
 
 
-def _zero1_worker(rank, world, port, out):
+def _zero1_worker(rank, world, port, out, modes=("nccl",)):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -84,7 +84,7 @@ def _zero1_worker(rank, world, port, out):
         gen = torch.Generator(device=dev).manual_seed(100 + rank)       # every rank has its own local gradients
         local = [[(torch.randn(s, generator=gen, device=dev) * 1e-2).bfloat16() for s in SHAPES] for _ in range(steps)]
         finals = {}
-        for captured in (False, True):
+        for mode, captured in [(m, c) for m in modes for c in (False, True)]:
             sp = ShardedParams(SHAPES, torch.bfloat16, dev, world, rank, buckets=2)
             wgen = torch.Generator(device=dev).manual_seed(3)
             for v in sp.views:
@@ -93,7 +93,7 @@ def _zero1_worker(rank, world, port, out):
             params = {i: torch.nn.Parameter(sp.views[i]) for i in sp.owned}
             for i, p in params.items():
                 p.grad = gviews[i]
-            st = ShardedStepper(sp, params, lambda ps: came_b200.CAME8bit(ps, lr=1e-3, weight_decay=1e-2), gather_mode="nccl")
+            st = ShardedStepper(sp, params, lambda ps: came_b200.CAME8bit(ps, lr=1e-3, weight_decay=1e-2), gather_mode=mode)
             for o in st.opts:
                 if o is not None:
                     o.param_groups[0]["grad_scale"] = 1.0 / world          # mean of the ranks' gradients
@@ -111,10 +111,14 @@ def _zero1_worker(rank, world, port, out):
                 else:
                     z.run()
             torch.cuda.synchronize()
-            finals[captured] = sp.flat.clone()
+            finals[(mode, captured)] = sp.flat.clone()
+            if captured and (mode, captured) != (modes[-1], True):
+                z.graph.reset()
+                z.graph = None
             dist.barrier()
-        same = torch.equal(finals[False], finals[True])
-        moved = not torch.equal(finals[True], torch.zeros_like(finals[True]))
+        first = finals[(modes[0], False)]
+        same = all(torch.equal(first, v) for v in finals.values())
+        moved = not torch.equal(first, torch.zeros_like(first))
         flag = torch.tensor([1.0 if (same and moved) else 0.0], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         ok = bool(flag.item() == 1.0)
@@ -141,6 +145,26 @@ def test_captured_zero1_sequence_equals_eager():
     out = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_zero1_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    for p in procs:
+        if p.is_alive():          # never by pattern: these are the exact processes started above
+            p.terminate()
+        assert p.exitcode == 0
+    assert out.get(timeout=10) is True
+
+
+def test_captured_zero1_sequence_with_the_exchange_fused_into_the_step():
+    """The same sequence with a stepper in push mode (the step's kernels store the new weights into the peer's buffer;
+    one small all-reduce instead of the all-gather), eager and captured, against the NCCL form."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_zero1_worker, args=(r, 2, port, out, ("nccl", "push"))) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
