@@ -586,11 +586,14 @@ int came_b200_plan_create(const CameTensorDesc* descs, int n_tensors, void* work
 void came_b200_plan_destroy(came_plan_t* plan) { delete plan; }
 
 // push mode: the whole parameter must lie inside the local buffer the peers mirror
-static bool pushed_param_in_range(const came_plan& plan, const CameTensorDesc& d) {
+static bool param_in_range(uintptr_t buf_lo, uintptr_t buf_hi, const CameTensorDesc& d) {
     const uintptr_t lo = reinterpret_cast<uintptr_t>(d.p);
     const uintptr_t bytes = (uintptr_t)d.rows * (uintptr_t)(d.cols ? d.cols : 1) * (uintptr_t)(d.batch > 1 ? d.batch : 1) *
                             (uintptr_t)elem_bytes(d.p_dtype);
-    return lo >= plan.push_lo && lo + bytes <= plan.push_hi;
+    return lo >= buf_lo && lo + bytes <= buf_hi;
+}
+static bool pushed_param_in_range(const came_plan& plan, const CameTensorDesc& d) {
+    return param_in_range(plan.push_lo, plan.push_hi, d);
 }
 
 int came_b200_plan_set_push(came_plan_t* plan, const void* local_base, size_t local_bytes, void* const* peer_bases, int n_peers) {
@@ -598,21 +601,19 @@ int came_b200_plan_set_push(came_plan_t* plan, const void* local_base, size_t lo
     if (n_peers == 0) { plan->n_push = 0; return CAME_OK; }
     if (n_peers < 0 || n_peers > MAX_PUSH_PEERS) return fail(CAME_E_INVALID, "plan_set_push: %d peers outside [0, %d]", n_peers, MAX_PUSH_PEERS);
     if (!local_base || !peer_bases || local_bytes == 0) return fail(CAME_E_INVALID, "plan_set_push: null argument");
-    came_plan probe;
-    probe.push_lo = reinterpret_cast<uintptr_t>(local_base);
-    probe.push_hi = probe.push_lo + local_bytes;
-    if (probe.push_lo % 16 != 0) return fail(CAME_E_INVALID, "plan_set_push: the local buffer is not 16-byte aligned");
+    const uintptr_t buf_lo = reinterpret_cast<uintptr_t>(local_base), buf_hi = buf_lo + local_bytes;
+    if (buf_lo % 16 != 0) return fail(CAME_E_INVALID, "plan_set_push: the local buffer is not 16-byte aligned");
     for (int i = 0; i < plan->n_tensors; ++i)
-        if (plan->fused[i] && !pushed_param_in_range(probe, plan->descs[i]))
+        if (plan->fused[i] && !param_in_range(buf_lo, buf_hi, plan->descs[i]))
             return fail(CAME_E_INVALID, "plan_set_push: tensor %d does not lie inside the local buffer", i);
     long long delta[MAX_PUSH_PEERS];
     for (int k = 0; k < n_peers; ++k) {
         const uintptr_t pb = reinterpret_cast<uintptr_t>(peer_bases[k]);
         if (!pb || pb % 16 != 0) return fail(CAME_E_INVALID, "plan_set_push: peer buffer %d is null or not 16-byte aligned", k);
-        if (pb < probe.push_hi && pb + local_bytes > probe.push_lo) return fail(CAME_E_INVALID, "plan_set_push: peer buffer %d overlaps the local one", k);
-        delta[k] = (long long)(pb - probe.push_lo);      // modular: the kernel adds it to a local address
+        if (pb < buf_hi && pb + local_bytes > buf_lo) return fail(CAME_E_INVALID, "plan_set_push: peer buffer %d overlaps the local one", k);
+        delta[k] = (long long)(pb - buf_lo);      // modular: the kernel adds it to a local address
     }
-    plan->push_lo = probe.push_lo; plan->push_hi = probe.push_hi;
+    plan->push_lo = buf_lo; plan->push_hi = buf_hi;
     for (int k = 0; k < n_peers; ++k) plan->push_delta[k] = delta[k];
     plan->n_push = n_peers;
     return CAME_OK;
